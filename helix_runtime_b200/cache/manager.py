@@ -48,6 +48,7 @@ class KvNeed:
     kv_heads: int
     head_dim: int
     window: Optional[int] = None     # None: every earlier key stays live
+    keep_first: int = 0              # with a window: the first keys stay live behind it
 
 
 @dataclasses.dataclass(frozen=True)
@@ -233,13 +234,21 @@ class CacheManager:
         for group in self.groups:
             window = group.need.window
             live = rows if window is None else \
-                min(rows, window + (1 + self.window_slack_pages) * self.page_size)
+                min(rows, window + (1 + self.window_slack_pages) * self.page_size
+                    + self.kept_pages(group) * self.page_size)
             needed.append(self.pages_for(live))
         return needed
 
+    def kept_pages(self, group: CacheGroup) -> int:
+        """Leading pages of a windowed group that hold keys every later position still sees
+        (``KvNeed.keep_first``): they are never given back while the request lives."""
+        if group.need.window is None:
+            return 0
+        return self.pages_for(group.need.keep_first)
+
     def first_page_seen(self, group: CacheGroup, length: int) -> int:
-        """Index of the first page that the query at position ``length`` still reads in
-        ``group``: 0 without a window."""
+        """Index of the first page that the window of the query at position ``length`` still
+        reaches in ``group``: 0 without a window.  (Kept first pages lie before it.)"""
         window = group.need.window
         if window is None:
             return 0
@@ -330,9 +339,10 @@ class CacheManager:
             # the next query sits at position new_length and reads keys >= new_length-window+1
             dead_pages = max(0, self.first_page_seen(group, new_length) - self.window_slack_pages)
             table = record.tables[index]
-            first = record.first_live[index]
+            # pages in front of `first_live` are gone but for the kept first ones
+            first = max(record.first_live[index], self.kept_pages(group))
             if dead_pages > first:
-                gone = [table[i] for i in range(first, dead_pages)]
+                gone = [table[i] for i in range(first, dead_pages) if table[i] >= 0]
                 self._give_back(group, gone)
                 for i in range(first, dead_pages):
                     table[i] = -1
@@ -415,7 +425,9 @@ class CacheManager:
                 raise ValueError(
                     f"group {group.index}: the source has given back pages that a request at "
                     f"{tokens} tokens still reads (window {group.need.window})")
-            shared.append([-1] * first + list(parent.tables[index][first:count]))
+            kept = min(self.kept_pages(group), first, count)
+            shared.append(list(parent.tables[index][:kept]) + [-1] * (first - kept)
+                          + list(parent.tables[index][first:count]))
         return shared
 
     def _state_at(self, parent: RequestCache, tokens: int) -> Optional[Dict[int, torch.Tensor]]:
@@ -440,7 +452,9 @@ class CacheManager:
             pages = shared[index][:count]
             group.pool.share([page for page in pages if page >= 0])
             record.tables[index] = list(pages)
-            record.first_live[index] = next((i for i, page in enumerate(pages) if page >= 0), count)
+            behind = self.kept_pages(group)     # the first gap comes behind the kept pages
+            record.first_live[index] = next(
+                (i for i, page in enumerate(pages) if page >= 0 and i >= behind), count)
             group.host_tables[slot, :count] = pages
             group.dirty = True
         record.length = tokens

@@ -1,7 +1,7 @@
 """One registry from an architecture's name to its configuration class and model spec.
 
 ``config.json`` chooses the model everywhere in the engine: ``architectures[0]``
-is looked up first, then ``model_type``.  The reference has only the gate
+is looked up first, then ``architecture`` (a single name), then ``model_type``.  The reference has only the gate
 ``model_type == "llama"`` (tools/convert_hf_llama.py:105-106) and a model-kind
 code in its file header (src/model/format.cpp:44); the registry generalises that
 gate so a second architecture is one ``register_architecture`` call.
@@ -55,6 +55,9 @@ def architecture_for(document: Mapping[str, Any]) -> Architecture:
     candidates = []
     if isinstance(names, list):
         candidates.extend(name for name in names if isinstance(name, str))
+    single = document.get("architecture")      # configurations that name one class as a string
+    if isinstance(single, str):
+        candidates.append(single)
     model_type = document.get("model_type")
     if isinstance(model_type, str):
         candidates.append(model_type)
@@ -63,7 +66,8 @@ def architecture_for(document: Mapping[str, Any]) -> Architecture:
         if entry is not None:
             return entry
     raise ConfigError(
-        f"no registered architecture for architectures={names!r} model_type={model_type!r}; "
+        f"no registered architecture for architectures={names if names is not None else single!r} "
+        f"model_type={model_type!r}; "
         f"known: {', '.join(known_architectures()) or '(none)'}")
 
 

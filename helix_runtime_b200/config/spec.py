@@ -39,7 +39,8 @@ class BlockSpec:
 
     ``arrangement`` names how the parts are wired, a key of the arrangement registry
     (``models.decoder.register_arrangement``); ``pre_norm`` is
-    ``x += mixer(norm(x)); x += ff(norm(x))`` (src/model/cpu_llama.cpp:62-98).  A block whose
+    ``x += mixer(norm(x)); x += ff(norm(x))`` (src/model/cpu_llama.cpp:62-98), ``parallel`` is
+    ``h = norm(x); x += mixer(h) + ff(h)`` (one norm, both sublayers read its output).  A block whose
     arrangement has no feed-forward, or no second norm, leaves those fields ``None``.
     """
 
@@ -56,11 +57,15 @@ class ScheduleEntry:
 
     ``cache_from`` is the index of an earlier schedule entry whose key/value
     cache (or state) this entry reads instead of owning one; ``None`` means the
-    entry owns its cache.
+    entry owns its cache.  ``add_embedding``: before this entry runs, the embedding's output
+    (the residual stream as it stood before the first entry) is added to the residual stream
+    once more; models that run a stretch of layers several times feed the input back in at
+    the start of every repeat.
     """
 
     block: int
     cache_from: Optional[int] = None
+    add_embedding: bool = False
 
 
 @dataclasses.dataclass(frozen=True)

@@ -23,6 +23,7 @@ from typing import List, Optional
 CSRC = os.path.dirname(os.path.abspath(__file__))
 SOURCES = (
     "hx_elementwise.cu",
+    "hx_short_conv.cu",
     "hx_gemm_simt.cu",
     "hx_gemm_tc.cu",
     "hx_attention.cu",

@@ -73,6 +73,7 @@ struct AttentionArgs {
   int page_size;
   int num_pages;
   int window;       // 0: every earlier key
+  int keep_first;   // with a window: keys at positions below this stay visible behind it
   float scale;
   int split_keys;
   int max_splits;
@@ -91,10 +92,18 @@ __device__ __forceinline__ void key_range(const AttentionArgs& a, int token, int
   lo = a.window > 0 ? max(0, hi - a.window) : 0;
 }
 
+// With kept first keys a row sees [0, kept) and [lo, hi), kept = min(keep_first, lo).  The
+// kernel walks them as ONE list of kept + hi - lo places: place v is key v below `kept` and
+// key lo + v - kept from there on.
+__device__ __forceinline__ int kept_keys(const AttentionArgs& a, int lo) {
+  return min(a.keep_first, lo);
+}
+
 // Which (token, head, split) is this warp's, and which keys does it walk?  False: nothing to do.
 struct Item {
   long long token_head;
   int token, head, split, n_splits, begin, end;
+  int kept, lo;     // place v of [begin, end) is key v below `kept`, key lo + v - kept above
 };
 
 __device__ __forceinline__ bool find_item(const AttentionArgs& a, long long index, Item& item) {
@@ -107,12 +116,17 @@ __device__ __forceinline__ bool find_item(const AttentionArgs& a, long long inde
   if (skipped(a, item.token)) return false;
   int lo, hi;
   key_range(a, item.token, lo, hi);
+  // begin and end count places of the row's list of visible keys (see kept_keys): without
+  // kept keys place v is key lo + v
+  item.kept = kept_keys(a, lo);
+  item.lo = lo;
+  const int places = item.kept + hi - lo;
   // a caller whose split sizes do not cover the context (split_keys * max_splits keys) gets
   // fewer, longer splits: the last one walks on to the end of the context
-  item.n_splits = min((hi - lo + a.split_keys - 1) / a.split_keys, a.max_splits);
+  item.n_splits = min((places + a.split_keys - 1) / a.split_keys, a.max_splits);
   if (item.split >= item.n_splits) return false;
-  item.begin = lo + item.split * a.split_keys;
-  item.end = item.split == item.n_splits - 1 ? hi : item.begin + a.split_keys;
+  item.begin = item.split * a.split_keys;
+  item.end = item.split == item.n_splits - 1 ? places : item.begin + a.split_keys;
   return true;
 }
 
@@ -240,8 +254,9 @@ __global__ __launch_bounds__(WARPS_PER_BLOCK * 32) void paged_attention_kernel(A
   const int my_dim = lane * DPL;
 
   for (int chunk = item.begin; chunk < item.end; chunk += 32) {
-    const int key = chunk + lane;
-    bool valid = key < item.end;
+    const int place = chunk + lane;
+    bool valid = place < item.end;
+    const int key = place < item.kept ? place : item.lo + place - item.kept;
     int page = -1, slot = 0;
     if (valid) {
       page = table[key / a.page_size];
@@ -1002,14 +1017,19 @@ HX_API long long hx_paged_attention_scratch_floats_for(int dtype, int tokens, in
   return hx_paged_attention_scratch_floats(tokens, heads, head_dim, max_splits);
 }
 
-HX_API int hx_paged_attention(const void* q, int ldq, const void* k_cache, const void* v_cache,
-                              int dtype, const int* positions, const int* token_request,
-                              const int* request_table_row, const int* block_tables,
-                              int table_stride, const int* request_start, int skip_query_len,
-                              void* out, int ldo, float* partial, int* arrivals, int tokens,
-                              int heads, int kv_heads, int head_dim, int page_size, int num_pages,
-                              int window, float scale, int split_keys, int max_splits, int* status,
-                              cudaStream_t stream) {
+// hx_paged_attention with kept first keys: a row at position p sees key j <= p when
+// p - j < window or j < keep_first (window 0: every earlier key, keep_first is then unused).
+HX_API int hx_paged_attention_kept(const void* q, int ldq, const void* k_cache, const void* v_cache,
+                                   int dtype, const int* positions, const int* token_request,
+                                   const int* request_table_row, const int* block_tables,
+                                   int table_stride, const int* request_start, int skip_query_len,
+                                   void* out, int ldo, float* partial, int* arrivals, int tokens,
+                                   int heads, int kv_heads, int head_dim, int page_size,
+                                   int num_pages, int window, int keep_first, float scale,
+                                   int split_keys, int max_splits, int* status,
+                                   cudaStream_t stream) {
+  HX_REQUIRE(keep_first >= 0, "hx_paged_attention: keep_first must not be negative");
+  if (window == 0) keep_first = 0;
   HX_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
              "hx_paged_attention: heads %d must be a positive multiple of kv_heads %d", heads,
              kv_heads);
@@ -1026,8 +1046,8 @@ HX_API int hx_paged_attention(const void* q, int ldq, const void* k_cache, const
   if (tokens == 0) return HX_OK;
   AttentionArgs a{q, ldq, k_cache, v_cache, positions, token_request, request_table_row,
                   block_tables, table_stride, request_start, skip_query_len, out, ldo, partial,
-                  arrivals, tokens, heads, kv_heads, head_dim, page_size, num_pages, window, scale,
-                  split_keys, max_splits, status};
+                  arrivals, tokens, heads, kv_heads, head_dim, page_size, num_pages, window,
+                  keep_first, scale, split_keys, max_splits, status};
   const long long items = static_cast<long long>(tokens) * heads * max_splits;
   HX_REQUIRE(items / STREAM_WARPS < (1ll << 31) - 1, "hx_paged_attention: grid too large");
   int rc;
@@ -1041,6 +1061,21 @@ HX_API int hx_paged_attention(const void* q, int ldq, const void* k_cache, const
   if (rc != HX_OK) return rc;
   HX_CHECK_LAUNCH("hx_paged_attention");
   return HX_OK;
+}
+
+HX_API int hx_paged_attention(const void* q, int ldq, const void* k_cache, const void* v_cache,
+                              int dtype, const int* positions, const int* token_request,
+                              const int* request_table_row, const int* block_tables,
+                              int table_stride, const int* request_start, int skip_query_len,
+                              void* out, int ldo, float* partial, int* arrivals, int tokens,
+                              int heads, int kv_heads, int head_dim, int page_size, int num_pages,
+                              int window, float scale, int split_keys, int max_splits, int* status,
+                              cudaStream_t stream) {
+  return hx_paged_attention_kept(q, ldq, k_cache, v_cache, dtype, positions, token_request,
+                                 request_table_row, block_tables, table_stride, request_start,
+                                 skip_query_len, out, ldo, partial, arrivals, tokens, heads,
+                                 kv_heads, head_dim, page_size, num_pages, window, 0, scale,
+                                 split_keys, max_splits, status, stream);
 }
 
 // ------------------------------------------------ the same attention, scratch built in

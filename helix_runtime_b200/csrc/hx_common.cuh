@@ -224,3 +224,32 @@ __device__ __forceinline__ float hx_silu(float x) {
 __device__ __forceinline__ float hx_silu_fast(float x) {
   return x >= 0.0f ? __fdividef(x, 1.0f + __expf(-x)) : __fdividef(x * __expf(x), 1.0f + __expf(x));
 }
+
+// What a gated feed-forward passes its gate through before the product with the up
+// projection.  gelu_tanh(z) = 0.5 z (1 + tanh(u)), u = sqrt(2/pi) (z + 0.044715 z^3); since
+// 0.5 (1 + tanh(u)) = sigmoid(2u), it is z * sigmoid(2u) and shares the stable sigmoid.
+enum HxGateActivation : int { HX_GATE_SILU = 0, HX_GATE_GELU_TANH = 1 };
+
+__device__ __forceinline__ float hx_sigmoid(float x) {
+  if (x >= 0.0f) return 1.0f / (1.0f + expf(-x));
+  const float e = expf(x);
+  return e / (1.0f + e);
+}
+
+__device__ __forceinline__ float hx_gelu_tanh(float z) {
+  const float u = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+  return z * hx_sigmoid(2.0f * u);
+}
+
+__device__ __forceinline__ float hx_gelu_tanh_fast(float z) {
+  const float v = 1.5957691216057308f * (z + 0.044715f * z * z * z);
+  return v >= 0.0f ? __fdividef(z, 1.0f + __expf(-v)) : __fdividef(z * __expf(v), 1.0f + __expf(v));
+}
+
+__device__ __forceinline__ float hx_gate(float x, int activation) {
+  return activation == HX_GATE_GELU_TANH ? hx_gelu_tanh(x) : hx_silu(x);
+}
+
+__device__ __forceinline__ float hx_gate_fast(float x, int activation) {
+  return activation == HX_GATE_GELU_TANH ? hx_gelu_tanh_fast(x) : hx_silu_fast(x);
+}

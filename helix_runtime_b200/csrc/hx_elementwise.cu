@@ -71,7 +71,8 @@ HX_API int hx_sm_count() { return hx_device_sm_count(); }
 // (the reference's rule, src/kernels/cuda/embedding.cu:21-39).
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                             float* __restrict__ out, int hidden, int vocab, int* status) {
+                             float* __restrict__ out, int hidden, int vocab, int* status,
+                             float scale) {
   hx_pdl_prologue();
   const int token = blockIdx.x;
   const int id = ids[token];
@@ -94,28 +95,57 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
         const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&packed);
         const float2 a = __bfloat1622float2(pairs[0]), b = __bfloat1622float2(pairs[1]);
         const float2 c = __bfloat1622float2(pairs[2]), d = __bfloat1622float2(pairs[3]);
-        wide[2 * p] = make_float4(a.x, a.y, b.x, b.y);
-        wide[2 * p + 1] = make_float4(c.x, c.y, d.x, d.y);
+        wide[2 * p] = make_float4(a.x * scale, a.y * scale, b.x * scale, b.y * scale);
+        wide[2 * p + 1] = make_float4(c.x * scale, c.y * scale, d.x * scale, d.y * scale);
       }
       return;
     }
   }
-  for (int c = threadIdx.x; c < hidden; c += blockDim.x) row_out[c] = hx_to_float<T>(row[c]);
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+    row_out[c] = hx_to_float<T>(row[c]) * scale;
 }
 
-HX_API int hx_embed(const void* table, int dtype, const int* ids, float* out, int tokens,
-                    int hidden, int vocab, int* status, cudaStream_t stream) {
+// out[t, :] = table[id[t], :] * scale: the table's value widened to float32, the product in
+// float32 (a scale of 1 changes no bit).
+HX_API int hx_embed_scaled(const void* table, int dtype, const int* ids, float* out, int tokens,
+                           int hidden, int vocab, float scale, int* status, cudaStream_t stream) {
   HX_REQUIRE(tokens >= 0 && hidden > 0 && vocab > 0, "hx_embed: bad sizes");
   if (tokens == 0) return HX_OK;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (dtype == HX_F32) {
-    hx_launch(embed_kernel<float>, tokens, threads, 0, stream, static_cast<const float*>(table), ids, out, hidden, vocab, status);
+    hx_launch(embed_kernel<float>, tokens, threads, 0, stream, static_cast<const float*>(table), ids, out, hidden, vocab, status, scale);
   } else if (dtype == HX_BF16) {
-    hx_launch(embed_kernel<__nv_bfloat16>, tokens, threads, 0, stream,  static_cast<const __nv_bfloat16*>(table), ids, out, hidden, vocab, status);
+    hx_launch(embed_kernel<__nv_bfloat16>, tokens, threads, 0, stream,  static_cast<const __nv_bfloat16*>(table), ids, out, hidden, vocab, status, scale);
   } else {
     HX_REQUIRE(false, "hx_embed: unknown dtype %d", dtype);
   }
   HX_CHECK_LAUNCH("hx_embed");
+  return HX_OK;
+}
+
+HX_API int hx_embed(const void* table, int dtype, const int* ids, float* out, int tokens,
+                    int hidden, int vocab, int* status, cudaStream_t stream) {
+  return hx_embed_scaled(table, dtype, ids, out, tokens, hidden, vocab, 1.0f, status, stream);
+}
+
+// x[t, :] += y[t, :] in float32 (a kept copy of the embedding output added back into the
+// residual stream before a repeated run of layers).
+__global__ void add_rows_kernel(float* __restrict__ x, const float* __restrict__ y, size_t total) {
+  hx_pdl_prologue();
+  for (size_t index = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; index < total;
+       index += static_cast<size_t>(gridDim.x) * blockDim.x)
+    x[index] += y[index];
+}
+
+HX_API int hx_add_rows(float* x, const float* y, int tokens, int hidden, cudaStream_t stream) {
+  HX_REQUIRE(tokens >= 0 && hidden > 0, "hx_add_rows: bad sizes");
+  if (tokens == 0) return HX_OK;
+  const size_t total = static_cast<size_t>(tokens) * hidden;
+  const size_t resident = static_cast<size_t>(hx_device_sm_count() > 0 ? hx_device_sm_count() : 1) * 16;
+  const size_t wanted = (total + 255) / 256;
+  hx_launch(add_rows_kernel, static_cast<int>(wanted < resident ? wanted : resident), 256, 0, stream,
+            x, y, total);
+  HX_CHECK_LAUNCH("hx_add_rows");
   return HX_OK;
 }
 
@@ -247,6 +277,90 @@ HX_API int hx_rmsnorm(const float* x, const float* weight, void* y, int out_dtyp
   return HX_OK;
 }
 
+// ------------------------------------------------------------------- LayerNorm
+
+// y = (x - mean) / sqrt(var + eps) * w + b with var the mean of the squared deviations, all in
+// float32.  One block per row; the row is read into registers once where it fits (widths to
+// LN_PER_THREAD * blockDim), else it is read three times.  Mean first, deviations second: the
+// variance is never a difference of two large sums.
+constexpr int LN_PER_THREAD = 16;
+
+template <typename TOut>
+__global__ __launch_bounds__(256) void layernorm_kernel(
+    const float* __restrict__ x, const float* __restrict__ weight, const float* __restrict__ bias,
+    TOut* __restrict__ y, const int* __restrict__ rows, int hidden, float eps) {
+  __shared__ float scratch[32];
+  hx_pdl_prologue();
+  const int out_row = blockIdx.x;
+  const int in_row = rows != nullptr ? rows[out_row] : out_row;
+  const float* xr = x + static_cast<size_t>(in_row) * hidden;
+  TOut* yr = y + static_cast<size_t>(out_row) * hidden;
+  const bool held = hidden <= LN_PER_THREAD * static_cast<int>(blockDim.x);
+  float value[LN_PER_THREAD];
+  float sum = 0.0f;
+  if (held) {
+#pragma unroll
+    for (int i = 0; i < LN_PER_THREAD; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      value[i] = c < hidden ? xr[c] : 0.0f;
+      sum += value[i];
+    }
+  } else {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) sum += xr[c];
+  }
+  const float mean = hx_block_sum(sum, scratch) / static_cast<float>(hidden);
+  float squares = 0.0f;
+  if (held) {
+#pragma unroll
+    for (int i = 0; i < LN_PER_THREAD; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      const float d = c < hidden ? value[i] - mean : 0.0f;
+      squares = fmaf(d, d, squares);
+    }
+  } else {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      const float d = xr[c] - mean;
+      squares = fmaf(d, d, squares);
+    }
+  }
+  const float variance = hx_block_sum(squares, scratch) / static_cast<float>(hidden);
+  const float inverse = 1.0f / sqrtf(variance + eps);
+  if (held) {
+#pragma unroll
+    for (int i = 0; i < LN_PER_THREAD; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < hidden)
+        yr[c] = hx_from_float<TOut>((value[i] - mean) * inverse * weight[c] +
+                                    (bias != nullptr ? bias[c] : 0.0f));
+    }
+  } else {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+      yr[c] = hx_from_float<TOut>((xr[c] - mean) * inverse * weight[c] +
+                                  (bias != nullptr ? bias[c] : 0.0f));
+  }
+}
+
+// bias may be null (a layer norm with a weight only).  `rows` as for hx_rmsnorm.
+HX_API int hx_layernorm(const float* x, const float* weight, const float* bias, void* y,
+                        int out_dtype, const int* rows, int n_rows, int hidden, float eps,
+                        cudaStream_t stream) {
+  HX_REQUIRE(n_rows >= 0 && hidden > 0, "hx_layernorm: bad sizes");
+  HX_REQUIRE(eps >= 0.0f, "hx_layernorm: eps must not be negative");
+  if (n_rows == 0) return HX_OK;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (out_dtype == HX_F32) {
+    hx_launch(layernorm_kernel<float>, n_rows, threads, 0, stream, x, weight, bias,
+              static_cast<float*>(y), rows, hidden, eps);
+  } else if (out_dtype == HX_BF16) {
+    hx_launch(layernorm_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, x, weight, bias,
+              static_cast<__nv_bfloat16*>(y), rows, hidden, eps);
+  } else {
+    HX_REQUIRE(false, "hx_layernorm: unknown dtype %d", out_dtype);
+  }
+  HX_CHECK_LAUNCH("hx_layernorm");
+  return HX_OK;
+}
+
 // ---------------------------------------------------------------------- SwiGLU
 
 // act[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]; gate and up arrive as float32
@@ -255,7 +369,7 @@ HX_API int hx_rmsnorm(const float* x, const float* weight, void* y, int out_dtyp
 // the tensor-core product applies the same formula in its epilogue.
 template <typename TOut>
 __global__ void swiglu_kernel(float* __restrict__ gate_up, TOut* __restrict__ act, int tokens,
-                              int intermediate, int ld_in, int zero_input) {
+                              int intermediate, int ld_in, int zero_input, int activation) {
   hx_pdl_prologue();
   const size_t total = static_cast<size_t>(tokens) * intermediate;
   for (size_t index = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; index < total;
@@ -263,7 +377,7 @@ __global__ void swiglu_kernel(float* __restrict__ gate_up, TOut* __restrict__ ac
     const size_t t = index / intermediate;
     const int i = static_cast<int>(index - t * intermediate);
     float* row = gate_up + t * ld_in;
-    act[index] = hx_from_float<TOut>(hx_silu(row[i]) * row[intermediate + i]);
+    act[index] = hx_from_float<TOut>(hx_gate(row[i], activation) * row[intermediate + i]);
     if (zero_input) {      // the buffer is a split-K accumulator: leave it clear for its next use
       row[i] = 0.0f;
       row[intermediate + i] = 0.0f;
@@ -271,8 +385,12 @@ __global__ void swiglu_kernel(float* __restrict__ gate_up, TOut* __restrict__ ac
   }
 }
 
-HX_API int hx_swiglu(float* gate_up, void* act, int out_dtype, int tokens, int intermediate,
-                     int ld_in, int zero_input, cudaStream_t stream) {
+// activation: HX_GATE_SILU (SwiGLU) or HX_GATE_GELU_TANH.
+HX_API int hx_gated_activation(float* gate_up, void* act, int out_dtype, int tokens,
+                               int intermediate, int ld_in, int zero_input, int activation,
+                               cudaStream_t stream) {
+  HX_REQUIRE(activation == HX_GATE_SILU || activation == HX_GATE_GELU_TANH,
+             "hx_gated_activation: unknown activation %d", activation);
   HX_REQUIRE(tokens >= 0 && intermediate > 0 && ld_in >= 2 * intermediate, "hx_swiglu: bad sizes");
   if (tokens == 0) return HX_OK;
   const size_t total = static_cast<size_t>(tokens) * intermediate;
@@ -280,14 +398,20 @@ HX_API int hx_swiglu(float* gate_up, void* act, int out_dtype, int tokens, int i
   const size_t resident = static_cast<size_t>(hx_device_sm_count() > 0 ? hx_device_sm_count() : 1) * 16;
   const int blocks = static_cast<int>(total / threads + 1 < resident ? total / threads + 1 : resident);
   if (out_dtype == HX_F32) {
-    hx_launch(swiglu_kernel<float>, blocks, threads, 0, stream, gate_up, static_cast<float*>(act), tokens, intermediate, ld_in, zero_input);
+    hx_launch(swiglu_kernel<float>, blocks, threads, 0, stream, gate_up, static_cast<float*>(act), tokens, intermediate, ld_in, zero_input, activation);
   } else if (out_dtype == HX_BF16) {
-    hx_launch(swiglu_kernel<__nv_bfloat16>, blocks, threads, 0, stream,  gate_up, static_cast<__nv_bfloat16*>(act), tokens, intermediate, ld_in, zero_input);
+    hx_launch(swiglu_kernel<__nv_bfloat16>, blocks, threads, 0, stream,  gate_up, static_cast<__nv_bfloat16*>(act), tokens, intermediate, ld_in, zero_input, activation);
   } else {
     HX_REQUIRE(false, "hx_swiglu: unknown dtype %d", out_dtype);
   }
   HX_CHECK_LAUNCH("hx_swiglu");
   return HX_OK;
+}
+
+HX_API int hx_swiglu(float* gate_up, void* act, int out_dtype, int tokens, int intermediate,
+                     int ld_in, int zero_input, cudaStream_t stream) {
+  return hx_gated_activation(gate_up, act, out_dtype, tokens, intermediate, ld_in, zero_input,
+                             HX_GATE_SILU, stream);
 }
 
 // ---------------------------------------------- rotary encoding + cache append

@@ -64,7 +64,8 @@ __device__ __forceinline__ void load_weight_box(void* dst, const CUtensorMap* ma
 // BN token columns, 16 columns at a time.  With SwiGLU the up accumulator sits BN columns on.
 template <int BN, int EPI>
 __device__ __forceinline__ void write_tile(void* out, int ldo, int tokens, int features,
-                                           uint32_t lane_address, int feature, int token0) {
+                                           uint32_t lane_address, int feature, int token0,
+                                           int activation) {
   const bool feature_ok = feature < features;
 #pragma unroll 1
   for (int column = 0; column < BN; column += 16) {
@@ -75,7 +76,7 @@ __device__ __forceinline__ void write_tile(void* out, int ldo, int tokens, int f
       float up[16];
       tmem_load16(lane_address + BN + column, up);
 #pragma unroll
-      for (int j = 0; j < 16; ++j) acc[j] = hx_silu_fast(acc[j]) * up[j];
+      for (int j = 0; j < 16; ++j) acc[j] = hx_gate_fast(acc[j], activation) * up[j];
     }
     if (feature_ok) {
 #pragma unroll
@@ -132,6 +133,7 @@ struct GemmArgs {
   int k_blocks_per_split;
   int k_tiles;        // > 0: the weights are stored as tiles, this many along k
   int* status;
+  int activation;     // gated epilogue: what the gate passes through (HxGateActivation)
 };
 
 template <int BN, int EPI>
@@ -260,7 +262,7 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_kernel(
         tc_fence_after();
         const uint32_t lane_address = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
         write_tile<BN, EPI>(args.out, args.ldo, args.tokens, args.features, lane_address, feature,
-                            token0);
+                            token0, args.activation);
       }
     }
   }
@@ -349,6 +351,7 @@ struct PersistentArgs {
   RopeArgs rope;              // EPI_ROPE_APPEND only
   int whole_rounds;           // >= 0: the tiles behind this many whole rounds are shared out by
                               // k-blocks (add epilogue only); -1: every unit is a whole tile
+  int activation;             // gated epilogue: what the gate passes through (HxGateActivation)
 };
 
 // What a CTA works on at a time: a tile, or (`partial`) a run of k-blocks of a tile that
@@ -429,7 +432,7 @@ __device__ __forceinline__ void load_row_into_accumulator(const float* out, int 
 // the accumulator.  With SwiGLU the accumulator holds 128 gate columns, then 128 up columns.
 template <int EPI>
 __device__ __forceinline__ void write_row(void* out, int ldo, int features, uint32_t lane_address,
-                                          int token, int tokens, int feature0) {
+                                          int token, int tokens, int feature0, int activation) {
   using Element = typename std::conditional<EPI == EPI_STORE_BF16 || EPI == EPI_SWIGLU,
                                             __nv_bfloat16, float>::type;
   constexpr int kColumns = EPI == EPI_SWIGLU ? BM : 2 * BM;
@@ -444,7 +447,7 @@ __device__ __forceinline__ void write_row(void* out, int ldo, int features, uint
       float up[16];
       tmem_load16(lane_address + BM + column, up);
 #pragma unroll
-      for (int j = 0; j < 16; ++j) acc[j] = hx_silu_fast(acc[j]) * up[j];
+      for (int j = 0; j < 16; ++j) acc[j] = hx_gate_fast(acc[j], activation) * up[j];
     }
     if (token >= tokens) continue;
     Element* row = static_cast<Element*>(out) + static_cast<size_t>(token) * ldo + feature0 + column;
@@ -760,7 +763,7 @@ __global__ __launch_bounds__(THREADS) void gemm_tc_persistent_kernel(
         write_row<EPI>(args.out, args.ldo, args.features,
                        lane_base + buffer * Config::kBufferColumns,
                        unit.token_tile * BM + quarter * 32 + lane, args.tokens,
-                       unit.feature_tile * FEATURES);
+                       unit.feature_tile * FEATURES, args.activation);
       }
       // every lane's tcgen05.ld has completed (the loads are waited for where they are
       // issued): hand the accumulator back
@@ -975,7 +978,8 @@ HX_API int hx_gemm_tc_supports(int tokens, int features, int depth, int ldx, int
 }
 
 // x: [tokens, depth] bf16 (row stride ldx), w: [weight_rows, depth] bf16 (row stride ldw).
-// epilogue 0/1/2: `features` = weight_rows outputs per token.  epilogue 3 (SwiGLU): w is the
+// epilogue 0/1/2: `features` = weight_rows outputs per token.  epilogue 3 (SwiGLU; 5: the same
+// with gelu_tanh in place of silu): w is the
 // fused [gate; up] matrix, `features` = intermediate size, gate rows [0, features), up rows
 // [up_row_offset, up_row_offset + features).  k_splits > 1 only with epilogue 2.
 // weight_tiles != 0: w holds the matrix as [ceil(weight_rows / 128)][ceil(depth / 64)] tiles of
@@ -987,6 +991,12 @@ HX_API int hx_gemm_tc(const void* x, int ldx, int x_capacity_rows, const void* w
                       int epilogue, int up_row_offset, int k_splits, int weight_tiles, int* status,
                       cudaStream_t stream) {
   if (weight_tiles) ldw = 8;      // not a stride of anything here
+  // the gated epilogue by the gate's activation: 3 is silu(gate) * up, 5 gelu_tanh(gate) * up
+  int activation = HX_GATE_SILU;
+  if (epilogue == 5) {
+    epilogue = EPI_SWIGLU;
+    activation = HX_GATE_GELU_TANH;
+  }
   HX_REQUIRE(!weight_tiles || epilogue != EPI_SWIGLU || up_row_offset % BM == 0,
              "hx_gemm_tc: with tiled weights the up rows must start on a multiple of %d", BM);
   HX_REQUIRE(hx_gemm_tc_supports(tokens, features, depth, ldx, ldw),
@@ -1027,7 +1037,7 @@ HX_API int hx_gemm_tc(const void* x, int ldx, int x_capacity_rows, const void* w
 
   if (persistent) {
     PersistentArgs args{out, ldo, tokens, features, depth, up_row_offset, k_tiles, 0, 0,
-                        total_k_blocks, status, RopeArgs{}};
+                        total_k_blocks, status, RopeArgs{}, -1, activation};
     rc = launch_persistent_epilogue(epilogue, map_w, map_x, args, stream);
     if (rc != HX_OK) return rc;
     HX_CHECK_LAUNCH("hx_gemm_tc");
@@ -1036,7 +1046,8 @@ HX_API int hx_gemm_tc(const void* x, int ldx, int x_capacity_rows, const void* w
   if (k_splits > total_k_blocks) k_splits = total_k_blocks;
   const int per_split = (total_k_blocks + k_splits - 1) / k_splits;
   k_splits = (total_k_blocks + per_split - 1) / per_split;
-  GemmArgs args{out, ldo, tokens, features, depth, up_row_offset, per_split, k_tiles, status};
+  GemmArgs args{out, ldo, tokens, features, depth, up_row_offset, per_split, k_tiles, status,
+                activation};
   const dim3 grid((tokens + bn - 1) / bn, (features + BM - 1) / BM, k_splits);
   HX_REQUIRE(grid.y <= 65535, "hx_gemm_tc: too many features (%d)", features);
 

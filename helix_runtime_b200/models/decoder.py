@@ -12,6 +12,7 @@ import torch
 
 from ..cache.manager import CacheManager, KvNeed, StateNeed
 from ..config.spec import BlockSpec, ModelSpec
+from ..ops import library as ops
 from ..parts.base import (FeedForward, LayerCache, Mixer, Norm, StepContext, build_part)
 from ..weights.loader import TensorRequest
 
@@ -43,6 +44,19 @@ def _pre_norm(block: "Block", ctx: StepContext, cache: LayerCache, residual: tor
 
 
 register_arrangement("pre_norm", _pre_norm)
+
+
+def _parallel(block: "Block", ctx: StepContext, cache: LayerCache, residual: torch.Tensor,
+              normed: torch.Tensor) -> None:
+    # h = norm(x); x += mixer(h) + ff(h): one norm, both sublayers read its output and add
+    # into the float32 residual stream (the sum is taken as (x + mixer) + ff)
+    block.mixer_norm.forward(ctx, residual, normed)
+    block.mixer.forward(ctx, cache, normed, residual)
+    if block.feed_forward is not None:
+        block.feed_forward.forward(ctx, normed, residual)
+
+
+register_arrangement("parallel", _parallel)
 
 
 class Block:
@@ -88,6 +102,8 @@ class DecoderModel:
         self.lm_head = build_part("lm_head", spec.lm_head, spec.hidden_size)
         self.dtype: Optional[torch.dtype] = None
         self.device: Optional[torch.device] = None
+        # debugging hook: called with (schedule index, residual rows) after every entry
+        self.after_entry: Optional[Callable[[int, torch.Tensor], None]] = None
 
     # ------------------------------------------------------------------ weights
 
@@ -179,8 +195,17 @@ class DecoderModel:
         residual = ctx.workspace.get("model.residual", (ctx.capacity, h), torch.float32)
         normed = ctx.workspace.get("model.normed", (ctx.capacity, h), ctx.dtype)
         self.embedding.forward(ctx, residual)
+        embedded = None
+        if any(entry.add_embedding for entry in self.schedule):
+            # the embedding's output is kept for the entries that add it back in
+            embedded = ctx.workspace.get("model.embedded", (ctx.capacity, h), torch.float32)
+            self.embedding.forward(ctx, embedded)
         for index, entry in enumerate(self.schedule):
+            if entry.add_embedding:
+                ops.add_rows(residual, embedded, ctx.n_tokens)
             self.blocks[entry.block].forward(ctx, self.layer_cache(cache, index), residual, normed)
+            if self.after_entry is not None:
+                self.after_entry(index, residual[:ctx.n_tokens])
         if n_want == 0:
             return None
         wanted = ctx.workspace.get("model.wanted", (ctx.capacity, h), ctx.dtype)

@@ -22,6 +22,11 @@ EPI_STORE = 0        # compute dtype out
 EPI_STORE_F32 = 1    # float32 out
 EPI_ADD_F32 = 2      # float32 out += product
 EPI_SWIGLU = 3       # tensor-core kernel only
+EPI_GEGLU_TANH = 5   # tensor-core kernel only: gelu_tanh(gate) * up
+
+GATE_SILU = 0        # what a gated feed-forward passes its gate through
+GATE_GELU_TANH = 1
+GATE_ACTIVATIONS = {"silu": GATE_SILU, "gelu_tanh": GATE_GELU_TANH}
 
 FLAG_BAD_TOKEN = 1
 FLAG_BAD_PAGE = 2
@@ -48,6 +53,23 @@ def _declare(library: ctypes.CDLL) -> None:
     library.hx_sm_count.restype = _c_int
     library.hx_sm_count.argtypes = []
     library.hx_embed.argtypes = [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr]
+    library.hx_embed_scaled.argtypes = [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
+                                        _c_float, _c_ptr, _c_ptr]
+    library.hx_add_rows.argtypes = [_c_ptr, _c_ptr, _c_int, _c_int, _c_ptr]
+    library.hx_layernorm.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int,
+                                     _c_float, _c_ptr]
+    library.hx_gated_activation.argtypes = [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                            _c_int, _c_ptr]
+    library.hx_short_conv_append.argtypes = [
+        _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr,
+        _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
+        _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr]
+    library.hx_sigmoid_gate.argtypes = [_c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int,
+                                        _c_ptr, _c_int, _c_int, _c_ptr]
+    library.hx_paged_attention_kept.argtypes = [
+        _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr,
+        _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+        _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr]
     library.hx_rmsnorm.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_float, _c_ptr]
     library.hx_swiglu.argtypes = [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr]
     library.hx_rope_append.argtypes = [
@@ -98,7 +120,9 @@ def _declare(library: ctypes.CDLL) -> None:
     library.hx_bounded_wait_check.restype = _c_int
     for name in ("hx_embed", "hx_rmsnorm", "hx_swiglu", "hx_rope_append", "hx_gemm_simt",
                  "hx_gemm_tc", "hx_gemm_tc_supports", "hx_gemm_tc_token_tile",
-                 "hx_paged_attention", "hx_argmax", "hx_sample"):
+                 "hx_paged_attention", "hx_argmax", "hx_sample", "hx_embed_scaled",
+                 "hx_add_rows", "hx_layernorm", "hx_gated_activation", "hx_short_conv_append",
+                 "hx_sigmoid_gate", "hx_paged_attention_kept"):
         getattr(library, name).restype = _c_int
 
 
@@ -173,15 +197,47 @@ def _need(tensor: torch.Tensor, dtype: torch.dtype, name: str, last_dim_contiguo
         raise KernelError(f"{name} must be contiguous in its last dimension")
 
 
-def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
-    """out[t] (float32) = table[ids[t]]."""
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
+          scale: float = 1.0) -> None:
+    """out[t] (float32) = table[ids[t]] * scale."""
     _need(ids, torch.int32, "ids")
     _need(out, torch.float32, "out")
     vocab, hidden = table.shape
     tokens = ids.shape[0]
     assert table.is_contiguous() and out.is_contiguous() and out.shape[1] == hidden
-    _check(lib().hx_embed(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), out.data_ptr(),
-                          tokens, hidden, vocab, _ptr(status), _stream()))
+    _check(lib().hx_embed_scaled(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(),
+                                 out.data_ptr(), tokens, hidden, vocab, float(scale),
+                                 _ptr(status), _stream()))
+
+
+def add_rows(x: torch.Tensor, y: torch.Tensor, tokens: int) -> None:
+    """x[:tokens] += y[:tokens]; both float32 with the same row width."""
+    _need(x, torch.float32, "x")
+    _need(y, torch.float32, "y")
+    assert x.is_contiguous() and y.is_contiguous() and x.shape[1] == y.shape[1]
+    assert x.shape[0] >= tokens and y.shape[0] >= tokens
+    _check(lib().hx_add_rows(x.data_ptr(), y.data_ptr(), tokens, x.shape[1], _stream()))
+
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
+              out: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = (x[r'] - mean) / sqrt(var + eps) * weight + bias with r' = rows[r] or r and var
+    the mean of the squared deviations; x, weight and bias float32."""
+    _need(x, torch.float32, "x")
+    _need(weight, torch.float32, "weight")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+    assert x.is_contiguous() and out.is_contiguous()
+    hidden = x.shape[-1]
+    n_rows = out.shape[0]
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+        assert rows.shape[0] >= n_rows
+    else:
+        assert x.shape[0] >= n_rows
+    _check(lib().hx_layernorm(x.data_ptr(), weight.data_ptr(), _ptr(bias), out.data_ptr(),
+                              dtype_code(out.dtype), _ptr(rows), n_rows, hidden, float(eps),
+                              _stream()))
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
@@ -201,14 +257,66 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float
                             _ptr(rows), n_rows, hidden, float(eps), _stream()))
 
 
-def swiglu(gate_up: torch.Tensor, act: torch.Tensor, zero_input: bool = False) -> None:
-    """act[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]; gate_up float32, act compute dtype.
+def swiglu(gate_up: torch.Tensor, act: torch.Tensor, zero_input: bool = False,
+           activation: int = GATE_SILU) -> None:
+    """act[t, i] = f(gate_up[t, i]) * gate_up[t, I + i] with f = silu (or ``activation``:
+    GATE_GELU_TANH); gate_up float32, act compute dtype.
     ``zero_input`` clears what was read (gate_up is a split-K accumulator)."""
     tokens, intermediate = act.shape
     _need(gate_up, torch.float32, "gate_up")
     assert act.is_contiguous()
-    _check(lib().hx_swiglu(gate_up.data_ptr(), act.data_ptr(), dtype_code(act.dtype), tokens,
-                           intermediate, gate_up.stride(0), 1 if zero_input else 0, _stream()))
+    _check(lib().hx_gated_activation(gate_up.data_ptr(), act.data_ptr(), dtype_code(act.dtype),
+                                     tokens, intermediate, gate_up.stride(0),
+                                     1 if zero_input else 0, int(activation), _stream()))
+
+
+def short_conv_append(raw: Optional[torch.Tensor], accum: Optional[torch.Tensor],
+                      out: torch.Tensor, filter_taps: torch.Tensor, state: Optional[torch.Tensor],
+                      positions: torch.Tensor, token_request: torch.Tensor,
+                      request_slot: torch.Tensor, request_start: torch.Tensor,
+                      block_tables: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+                      v_cache: Optional[torch.Tensor], tokens: int, heads: int, kv_heads: int,
+                      head_dim: int, total: int, page_size: int, num_pages: int,
+                      status: torch.Tensor) -> None:
+    """Causal filter over time on the columns ``[q heads | k heads | v heads]`` of the
+    projected rows (``raw`` in the compute dtype, or ``accum``: their float32 sums, which are
+    NOT cleared), ``filter_taps`` float32 ``[channels, taps]`` with the last tap on the token
+    itself; ``state`` ``[slot, taps - 1, channels]`` holds each request's last projected values
+    and is updated.  Queries go to ``out``; keys and values to their pages when ``k_cache`` is
+    given, else to ``out`` too.  Columns from ``channels`` to ``total`` are copied to ``out``."""
+    _need(filter_taps, torch.float32, "filter_taps")
+    channels = (heads + 2 * kv_heads) * head_dim
+    taps = filter_taps.shape[1]
+    assert filter_taps.is_contiguous() and filter_taps.shape[0] == channels
+    if taps > 1:
+        assert state is not None and state.dtype == out.dtype and state.is_contiguous()
+        assert tuple(state.shape[1:]) == (taps - 1, channels)
+    if raw is not None:
+        assert raw.dtype == out.dtype and raw.stride(-1) == 1
+    if accum is not None:
+        _need(accum, torch.float32, "accum")
+    write = k_cache is not None
+    _check(lib().hx_short_conv_append(
+        _ptr(raw), 0 if raw is None else raw.stride(0), _ptr(accum),
+        0 if accum is None else accum.stride(0), out.data_ptr(), out.stride(0),
+        dtype_code(out.dtype), filter_taps.data_ptr(), _ptr(state), taps, positions.data_ptr(),
+        token_request.data_ptr(), request_slot.data_ptr(), request_start.data_ptr(),
+        _ptr(block_tables) if write else None, block_tables.stride(0) if write else 0,
+        _ptr(k_cache), _ptr(v_cache), 1 if write else 0, tokens, heads, kv_heads, head_dim, total,
+        page_size, num_pages, _ptr(status), _stream()))
+
+
+def sigmoid_gate(context: torch.Tensor, gate: torch.Tensor, tokens: int, width: int,
+                 clear: Optional[torch.Tensor] = None) -> None:
+    """context[:tokens, :width] *= sigmoid(gate[:tokens, :width]) (float32 product, one
+    rounding).  ``clear``: a float32 accumulator whose first ``tokens`` rows are zeroed."""
+    assert context.dtype == gate.dtype and context.stride(-1) == 1 and gate.stride(-1) == 1
+    if clear is not None:
+        _need(clear, torch.float32, "clear")
+    _check(lib().hx_sigmoid_gate(context.data_ptr(), context.stride(0), gate.data_ptr(),
+                                 gate.stride(0), dtype_code(context.dtype), tokens, width,
+                                 _ptr(clear), 0 if clear is None else clear.stride(0),
+                                 0 if clear is None else clear.shape[1], _stream()))
 
 
 def rope_append(qkv: torch.Tensor, positions: torch.Tensor, token_request: torch.Tensor,
@@ -346,10 +454,11 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                     head_dim: int, page_size: int, num_pages: int, window: int, scale: float,
                     split_keys: int, max_splits: int, status: torch.Tensor,
                     request_start: Optional[torch.Tensor] = None, skip_query_len: int = 0,
-                    arrivals: Optional[torch.Tensor] = None) -> None:
+                    arrivals: Optional[torch.Tensor] = None, keep_first: int = 0) -> None:
     """out[t, h*D:(h+1)*D] = attention of query (t, h) over its request's pages.  With
     ``skip_query_len > 0`` tokens of requests that bring at least that many tokens are left
-    out (the tensor-core kernel takes them).  The call needs scratch, made here when it is
+    out (the tensor-core kernel takes them).  With a window, keys at positions below
+    ``keep_first`` stay visible behind it.  The call needs scratch, made here when it is
     not given: ``partial`` (float32, :func:`attention_scratch_floats` elements) and
     ``arrivals`` (int32, one counter per (token, head), zero on entry; the kernel leaves it
     zero)."""
@@ -359,13 +468,13 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         partial = torch.empty(attention_scratch_floats(tokens, heads, head_dim, max_splits,
                                                        q.dtype, page_size, window),
                               dtype=torch.float32, device=q.device)
-    _check(lib().hx_paged_attention(
+    _check(lib().hx_paged_attention_kept(
         q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), dtype_code(q.dtype),
         positions.data_ptr(), token_request.data_ptr(), request_table_row.data_ptr(),
         block_tables.data_ptr(), block_tables.stride(0), _ptr(request_start), skip_query_len,
         out.data_ptr(), out.stride(0),
         _ptr(partial), _ptr(arrivals), tokens, heads, kv_heads, head_dim, page_size, num_pages, window,
-        float(scale), split_keys, max_splits, _ptr(status), _stream()))
+        int(keep_first), float(scale), split_keys, max_splits, _ptr(status), _stream()))
 
 
 PREFILL_TILE_ROWS = 64        # query rows of a CTA of the ``mma.sync`` prompt kernel

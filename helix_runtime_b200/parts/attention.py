@@ -6,6 +6,23 @@ keys), ``position`` (a position-encoding spec), ``checkpoint_pairing`` (how the
 checkpoint's q/k rows are ordered for rotation).  Tensors: ``q``, ``k``, ``v``
 ``[heads*head_dim, hidden]`` and ``o`` ``[hidden, heads*head_dim]``, all ``[out, in]``.
 
+Optional mechanisms, each a parameter (absent: as if it did not exist):
+
+* ``value_dim``: the size of a value head when it differs from ``head_dim`` (``v`` is then
+  ``[kv_heads*value_dim, hidden]``, ``o`` ``[hidden, heads*value_dim]``).  Heads are held in
+  rows of ``row_dim``, the kernels' size that holds the larger of the two, with exact zeros in
+  the coordinates a head does not have (see the last paragraph).
+* ``keep_first`` (with ``window``): position ``i`` sees ``j <= i`` when ``i - j < window`` or
+  ``j < keep_first``; the kept keys keep their pages when the window has passed them.
+* ``short_conv``: taps of a causal filter over time on every channel of q, k and v, applied
+  right after the projection (tensors ``q_conv``, ``k_conv``, ``v_conv`` ``[channels, taps]``,
+  the last tap on the token's own value).  The last ``taps - 1`` projected values of a request
+  are per-request state (``state_need``).  The filter kernel appends keys and values to the
+  pages itself when the position encoding is ``none``.
+* ``output_gate`` (``"sigmoid"``): the concatenated heads are multiplied by
+  ``sigmoid(g x)`` before the output projection (tensor ``g`` ``[heads*value_dim, hidden]``);
+  with a filter the gate's projection is part of the fused product.
+
 At load the three projections are fused into one ``[(A + 2 Akv) D, H]`` matrix and,
 when the checkpoint rotates half-split pairs while the encoding rotates adjacent
 pairs, the rows of q and k are permuted per head to ``[0, D/2, 1, D/2+1, ...]``
@@ -29,7 +46,7 @@ from typing import List, Mapping, Optional
 
 import torch
 
-from ..cache.manager import KvNeed
+from ..cache.manager import KvNeed, StateNeed
 from ..config.spec import PartSpec
 from ..ops import library as ops
 from ..weights.loader import TensorRequest
@@ -72,46 +89,84 @@ class PagedAttention(Mixer):
         self.scale = float(spec.get("scale") or 1.0 / math.sqrt(float(self.head_dim)))
         window = spec.get("window")
         self.window: Optional[int] = int(window) if window else None
+        self.keep_first = int(spec.get("keep_first") or 0) if self.window else 0
+        self.value_dim = int(spec.get("value_dim") or self.head_dim)
+        self.conv_taps = int(spec.get("short_conv") or 1)
+        if self.conv_taps < 1:
+            raise ValueError("short_conv counts the filter's taps: at least 1")
+        gate = spec.get("output_gate")
+        if gate not in (None, "sigmoid"):
+            raise ValueError(f"output gate {gate!r} has no kernel; only 'sigmoid'")
+        self.gated = gate is not None
         self.row_dim = self.head_dim
         self.position = build_part("position", spec["position"], hidden_size)
-        wide = row_width(self.head_dim)
-        if wide != self.head_dim:
+        wide = row_width(max(self.head_dim, self.value_dim))
+        if wide != self.head_dim or self.value_dim != self.head_dim:
             position = spec["position"]
             padded = build_part("position", PartSpec(position.kind,
                                                      {**position.params, "row_dim": wide},
                                                      position.tensors), hidden_size)
             if getattr(padded, "row_dim", None) == wide:
                 self.position, self.row_dim = padded, wide
+            elif self.value_dim != self.head_dim:
+                raise ValueError(f"position encoding {position.kind!r} takes no row width of its "
+                                 f"own, which heads of {self.head_dim} with values of "
+                                 f"{self.value_dim} need")
         self.checkpoint_pairing = spec.get("checkpoint_pairing", self.position.pairing)
         self.names = dict(spec.tensors)
         # widths of the checkpoint's matrices and of the rows this part computes with
         self.q_rows = self.heads * self.head_dim
         self.kv_rows = self.kv_heads * self.head_dim
+        self.v_rows = self.kv_heads * self.value_dim
+        self.o_columns = self.heads * self.value_dim
         self.q_size = self.heads * self.row_dim
         self.kv_size = self.kv_heads * self.row_dim
         self.qkv_size = self.q_size + 2 * self.kv_size
+        # with a filter the gate's projection rides in the fused product, behind q, k and v
+        self.fused_gate = self.gated and self.conv_taps > 1
+        self.projected_size = self.qkv_size + (self.q_size if self.fused_gate else 0)
+        # the filter kernel appends to the pages itself when nothing comes between
+        self.conv_appends = self.conv_taps > 1 and self.position.pairing is None \
+            and getattr(self.position, "rotary_dim", None) == 0
+        self.dtype = torch.float32
         self.w_qkv: Optional[Weight] = None
         self.w_o: Optional[Weight] = None
+        self.w_g: Optional[Weight] = None
+        self.conv_filter: Optional[torch.Tensor] = None
 
     def kv_need(self) -> Optional[KvNeed]:
-        return KvNeed(self.kv_heads, self.row_dim, self.window)
+        return KvNeed(self.kv_heads, self.row_dim, self.window, self.keep_first)
+
+    def state_need(self) -> Optional[StateNeed]:
+        if self.conv_taps <= 1:
+            return None
+        return StateNeed((self.conv_taps - 1, self.qkv_size), self.dtype)
 
     def tensor_requests(self) -> List[TensorRequest]:
         h = self.hidden_size
-        return [
+        requests = [
             TensorRequest(self.names["q"], (self.q_rows, h)),
             TensorRequest(self.names["k"], (self.kv_rows, h)),
-            TensorRequest(self.names["v"], (self.kv_rows, h)),
-            TensorRequest(self.names["o"], (h, self.q_rows)),
+            TensorRequest(self.names["v"], (self.v_rows, h)),
+            TensorRequest(self.names["o"], (h, self.o_columns)),
             *self.position.tensor_requests(),
         ]
+        if self.gated:
+            requests.append(TensorRequest(self.names["g"], (self.o_columns, h)))
+        if self.conv_taps > 1:
+            requests.extend(
+                TensorRequest(self.names[name], (rows, self.conv_taps), role="scale")
+                for name, rows in (("q_conv", self.q_rows), ("k_conv", self.kv_rows),
+                                   ("v_conv", self.v_rows)))
+        return requests
 
-    def widen_rows(self, matrix: torch.Tensor, heads: int) -> torch.Tensor:
+    def widen_rows(self, matrix: torch.Tensor, heads: int, head_dim: Optional[int] = None) -> torch.Tensor:
         """``[heads * head_dim, in]`` to ``[heads * row_dim, in]``: zero rows behind each head."""
-        if self.row_dim == self.head_dim:
+        head_dim = self.head_dim if head_dim is None else head_dim
+        if self.row_dim == head_dim:
             return matrix
         wide = matrix.new_zeros((heads, self.row_dim, matrix.shape[1]))
-        wide[:, :self.head_dim] = matrix.reshape(heads, self.head_dim, matrix.shape[1])
+        wide[:, :head_dim] = matrix.reshape(heads, head_dim, matrix.shape[1])
         return wide.reshape(heads * self.row_dim, matrix.shape[1])
 
     def bind(self, tensors: Mapping[str, torch.Tensor], dtype, device) -> None:
@@ -122,16 +177,38 @@ class PagedAttention(Mixer):
                 and self.checkpoint_pairing != self.position.pairing):
             if self.checkpoint_pairing == "half_split" and self.position.pairing == "adjacent":
                 rotary = self.position.rotary_dim
-                q = q[rotary_row_permutation(self.heads, self.head_dim, rotary).to(q.device)]
-                k = k[rotary_row_permutation(self.kv_heads, self.head_dim, rotary).to(k.device)]
+                q_order = rotary_row_permutation(self.heads, self.head_dim, rotary)
+                k_order = rotary_row_permutation(self.kv_heads, self.head_dim, rotary)
+                q = q[q_order.to(q.device)]
+                k = k[k_order.to(k.device)]
+                if self.conv_taps > 1:      # the filter's channels move with their rows
+                    tensors = dict(tensors)
+                    for name, order in (("q_conv", q_order), ("k_conv", k_order)):
+                        taps = tensors[self.names[name]]
+                        tensors[self.names[name]] = taps[order.to(taps.device)]
             else:
                 raise ValueError(f"no row permutation from {self.checkpoint_pairing!r} to "
                                  f"{self.position.pairing!r}")
         q, k, v = (self.widen_rows(q, self.heads), self.widen_rows(k, self.kv_heads),
-                   self.widen_rows(v, self.kv_heads))
-        o = self.widen_rows(tensors[self.names["o"]].t().contiguous(), self.heads).t()
-        self.w_qkv = Weight(torch.cat([q, k, v], dim=0).to(device=device, dtype=dtype).contiguous())
+                   self.widen_rows(v, self.kv_heads, self.value_dim))
+        o = self.widen_rows(tensors[self.names["o"]].t().contiguous(), self.heads,
+                            self.value_dim).t()
+        fused = [q, k, v]
+        if self.gated:
+            g = self.widen_rows(tensors[self.names["g"]], self.heads, self.value_dim)
+            if self.fused_gate:
+                fused.append(g)
+            else:
+                self.w_g = Weight(g.to(device=device, dtype=dtype).contiguous())
+        self.w_qkv = Weight(torch.cat(fused, dim=0).to(device=device, dtype=dtype).contiguous())
         self.w_o = Weight(o.to(device=device, dtype=dtype).contiguous())
+        if self.conv_taps > 1:
+            self.conv_filter = torch.cat([
+                self.widen_rows(tensors[self.names["q_conv"]], self.heads),
+                self.widen_rows(tensors[self.names["k_conv"]], self.kv_heads),
+                self.widen_rows(tensors[self.names["v_conv"]], self.kv_heads, self.value_dim),
+            ], dim=0).to(device=device, dtype=torch.float32).contiguous()
+        self.dtype = dtype
         self.position.bind(tensors, dtype, device)
 
     @property
@@ -139,7 +216,35 @@ class PagedAttention(Mixer):
         return self.position.graph_safe
 
     def weight_bytes(self) -> int:
-        return self.w_qkv.nbytes() + self.w_o.nbytes()
+        return (self.w_qkv.nbytes() + self.w_o.nbytes()
+                + (self.w_g.nbytes() if self.w_g is not None else 0))
+
+    def project_filtered(self, ctx: StepContext, cache: LayerCache, x: torch.Tensor,
+                         qkv: torch.Tensor) -> Optional[torch.Tensor]:
+        """Projection, causal filter over time and cache append.  Leaves the filtered queries
+        (and the gate's projection, when it is fused) in ``qkv``; returns the float32
+        accumulator the projection summed into, which is still to be cleared, or None."""
+        n = ctx.n_tokens
+        write = cache.owns and cache.keys is not None
+        appends = self.conv_appends and write
+        accumulator = raw = None
+        if is_weight_stream(x, self.w_qkv, n):
+            accumulator = ctx.workspace.accumulator("attention.projected",
+                                                    (STREAMING_MAX_TOKENS, self.projected_size))
+            project_into_accumulator(x, self.w_qkv, accumulator, n, ctx.status, ctx.ordered_sums)
+        else:
+            raw = ctx.workspace.get("attention.projected", (ctx.capacity, self.projected_size),
+                                    ctx.dtype)
+            project(x, self.w_qkv, raw, n, ops.EPI_STORE, ctx.status)
+        ops.short_conv_append(raw, accumulator, qkv, self.conv_filter, cache.state, ctx.positions,
+                              ctx.token_request, ctx.request_slot, ctx.request_start,
+                              cache.block_tables if appends else None,
+                              cache.keys if appends else None, cache.values if appends else None,
+                              n, self.heads, self.kv_heads, self.row_dim, self.projected_size,
+                              cache.page_size, cache.num_pages, ctx.status)
+        if not self.conv_appends:
+            self.position.apply(ctx, cache, qkv, self.heads, self.kv_heads)
+        return accumulator
 
     def split_keys_for(self, tokens: int, longest: int, limit: int) -> int:
         """Keys per split.  One warp walks one (token, head, split); a step with few tokens
@@ -155,9 +260,12 @@ class PagedAttention(Mixer):
     def forward(self, ctx: StepContext, cache: LayerCache, x: torch.Tensor,
                 residual: torch.Tensor) -> None:
         n = ctx.n_tokens
-        qkv = ctx.workspace.get("attention.qkv", (ctx.capacity, self.qkv_size), ctx.dtype)
+        qkv = ctx.workspace.get("attention.qkv", (ctx.capacity, self.projected_size), ctx.dtype)
         context = ctx.workspace.get("attention.context", (ctx.capacity, self.q_size), ctx.dtype)
-        if is_weight_stream(x, self.w_qkv, n):
+        uncleared = None
+        if self.conv_taps > 1:
+            uncleared = self.project_filtered(ctx, cache, x, qkv)
+        elif is_weight_stream(x, self.w_qkv, n):
             # few tokens: split-K into a float32 accumulator that the rotary kernel reads,
             # rounds as the product's store would have, and clears
             accumulator = ctx.workspace.accumulator("attention.qkv",
@@ -171,6 +279,7 @@ class PagedAttention(Mixer):
             self.position.apply(ctx, cache, qkv, self.heads, self.kv_heads)
 
         window = cache.window or 0
+        kept = self.keep_first if window else 0
         # prompt portions of at least TENSOR_CORE_MIN_QUERY tokens go to the tensor-core
         # kernel (bfloat16, no window, head sizes it has); the rest, decode tokens above all,
         # to the CUDA-core kernel.  A step may need both.
@@ -185,7 +294,8 @@ class PagedAttention(Mixer):
                                   self.scale, TENSOR_CORE_MIN_QUERY, ctx.status,
                                   query_lengths=ctx.host_query_lengths)
         if not tensor_cores or ctx.min_query_len < TENSOR_CORE_MIN_QUERY:
-            longest = ctx.max_context_len if not window else min(ctx.max_context_len, window)
+            longest = ctx.max_context_len if not window else \
+                min(ctx.max_context_len, window + kept)
             split_keys = self.split_keys_for(n, longest, ctx.attention_split_keys)
             max_splits = max(1, -(-longest // split_keys))
             floats = ops.attention_scratch_floats(n, self.heads, self.row_dim, max_splits,
@@ -199,7 +309,16 @@ class PagedAttention(Mixer):
                                 cache.num_pages, window, self.scale, split_keys, max_splits,
                                 ctx.status, request_start=ctx.request_start,
                                 skip_query_len=TENSOR_CORE_MIN_QUERY if tensor_cores else 0,
-                                arrivals=arrivals)
+                                arrivals=arrivals, keep_first=kept)
+        if self.gated:
+            if self.fused_gate:
+                gate = qkv[:, self.qkv_size:]
+            else:
+                gate = ctx.workspace.get("attention.gate", (ctx.capacity, self.q_size), ctx.dtype)
+                project(x, self.w_g, gate, n, ops.EPI_STORE, ctx.status)
+            ops.sigmoid_gate(context, gate, n, self.q_size, clear=uncleared)
+        elif uncleared is not None:
+            uncleared[:n].zero_()
         project(context, self.w_o, residual, n, ops.EPI_ADD_F32, ctx.status, ctx.ordered_sums)
 
 

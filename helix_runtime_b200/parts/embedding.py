@@ -1,6 +1,6 @@
 """Token embedding and the output head.
 
-Embedding: ``hidden[t] = table[id[t]]`` widened into the float32 residual stream
+Embedding: ``hidden[t] = table[id[t]] * scale`` widened into the float32 residual stream
 (src/model/cpu_llama.cpp:21-27, 49).  Head: ``logits = x @ head.T`` in float32
 (src/model/cpu_llama.cpp:107); when the checkpoint has no head tensor and ties its
 embeddings the table stands in (tools/convert_hf_llama.py:497-510).
@@ -22,6 +22,8 @@ class TokenEmbedding(Part):
     def __init__(self, spec: PartSpec, hidden_size: int) -> None:
         super().__init__(spec, hidden_size)
         self.vocab_size = int(spec["vocab_size"])
+        # the looked-up row times this constant, in float32 (1: the row as it is)
+        self.scale = float(spec.get("scale", 1.0))
         self.name = spec.tensors["weight"]
         self.table: Optional[torch.Tensor] = None
 
@@ -32,7 +34,8 @@ class TokenEmbedding(Part):
         self.table = tensors[self.name].to(device=device, dtype=dtype).contiguous()
 
     def forward(self, ctx: StepContext, residual: torch.Tensor) -> None:
-        ops.embed(self.table, ctx.token_ids[:ctx.n_tokens], residual[:ctx.n_tokens], ctx.status)
+        ops.embed(self.table, ctx.token_ids[:ctx.n_tokens], residual[:ctx.n_tokens], ctx.status,
+                  self.scale)
 
 
 class LmHead(Part):

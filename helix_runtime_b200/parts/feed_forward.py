@@ -1,9 +1,10 @@
 """Gated feed-forward: ``down(act(gate(x)) * up(x))`` (src/model/cpu_llama.cpp:93-98).
 
-Parameters: ``intermediate_size``, ``activation`` (``silu``).  Tensors: ``gate``, ``up``
+Parameters: ``intermediate_size``, ``activation`` (``silu``, or ``gelu_tanh``:
+``0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))``).  Tensors: ``gate``, ``up``
 ``[intermediate, hidden]`` and ``down`` ``[hidden, intermediate]``.  gate and up are
 fused into one ``[2I, H]`` matrix at load so that both products read the input once;
-on the tensor cores SwiGLU is the epilogue of that product.
+on the tensor cores the gated activation is the epilogue of that product.
 """
 from __future__ import annotations
 
@@ -23,8 +24,10 @@ class GatedMlp(FeedForward):
         super().__init__(spec, hidden_size)
         self.intermediate = int(spec["intermediate_size"])
         activation = spec.get("activation", "silu")
-        if activation != "silu":
-            raise ValueError(f"activation {activation!r} has no kernel; only 'silu'")
+        if activation not in ops.GATE_ACTIVATIONS:
+            raise ValueError(f"activation {activation!r} has no kernel; known: "
+                             + ", ".join(sorted(ops.GATE_ACTIVATIONS)))
+        self.activation = ops.GATE_ACTIVATIONS[activation]
         self.names = dict(spec.tensors)
         self.w_gate_up: Optional[Weight] = None
         self.w_down: Optional[Weight] = None
@@ -48,7 +51,7 @@ class GatedMlp(FeedForward):
         n = ctx.n_tokens
         act = ctx.workspace.get("mlp.act", (ctx.capacity, self.intermediate), ctx.dtype)
         project_swiglu(x, self.w_gate_up, self.intermediate, act, ctx.workspace, ctx.capacity, n,
-                       ctx.status, ctx.ordered_sums)
+                       ctx.status, ctx.ordered_sums, self.activation)
         project(act, self.w_down, residual, n, ops.EPI_ADD_F32, ctx.status, ctx.ordered_sums)
 
 

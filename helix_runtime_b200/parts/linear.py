@@ -131,8 +131,9 @@ def project_into_accumulator(x: torch.Tensor, w: Weight, accumulator: torch.Tens
 
 def project_swiglu(x: torch.Tensor, w_gate_up: Weight, intermediate: int, act: torch.Tensor,
                    workspace, capacity: int, tokens: int, status: torch.Tensor,
-                   ordered: bool = False) -> None:
-    """``act[:tokens] = silu(x @ gate.T) * (x @ up.T)`` with ``w_gate_up = [gate; up]``.
+                   ordered: bool = False, activation: int = ops.GATE_SILU) -> None:
+    """``act[:tokens] = f(x @ gate.T) * (x @ up.T)`` with ``w_gate_up = [gate; up]`` and ``f``
+    silu or what ``activation`` names (``ops.GATE_ACTIVATIONS``).
 
     Three routes, one rounding each (float32 gate and up, float32 activation, one store):
     many tokens on the tensor cores: SwiGLU is the product's epilogue; few tokens on the
@@ -143,11 +144,12 @@ def project_swiglu(x: torch.Tensor, w_gate_up: Weight, intermediate: int, act: t
     if is_weight_stream(x, w_gate_up, tokens):
         accumulator = workspace.accumulator("mlp.gate_up", (STREAMING_MAX_TOKENS, 2 * intermediate))
         project_into_accumulator(x, w_gate_up, accumulator, tokens, status, ordered)
-        ops.swiglu(accumulator[:tokens], act[:tokens], zero_input=True)
+        ops.swiglu(accumulator[:tokens], act[:tokens], zero_input=True, activation=activation)
     elif uses_tensor_cores(x, w_gate_up, tokens):
-        _gemm_tc(x, w_gate_up, act, tokens, intermediate, ops.EPI_SWIGLU, status,
+        epilogue = ops.EPI_GEGLU_TANH if activation == ops.GATE_GELU_TANH else ops.EPI_SWIGLU
+        _gemm_tc(x, w_gate_up, act, tokens, intermediate, epilogue, status,
                  up_row_offset=intermediate)
     else:
         scratch = workspace.get("mlp.gate_up", (capacity, 2 * intermediate), torch.float32)
         _gemm_simt(x, w_gate_up, scratch, tokens, ops.EPI_STORE_F32)
-        ops.swiglu(scratch[:tokens], act[:tokens])
+        ops.swiglu(scratch[:tokens], act[:tokens], activation=activation)

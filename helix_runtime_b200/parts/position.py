@@ -1,4 +1,5 @@
-"""Rotary position encoding with the cache append fused into the same kernel.
+"""Position encodings.  Rotary position encoding with the cache append fused into the same
+kernel, and :class:`NoPosition` (the append alone).
 
 Parameters: ``theta``, ``head_dim``, ``rotary_dim`` (default: all of the head),
 ``row_dim`` (default ``head_dim``: the width a head has in the projected rows and in the
@@ -90,4 +91,33 @@ class RotaryEncoding(PositionEncoding):
         return True
 
 
+class NoPosition(PositionEncoding):
+    """No position encoding: queries and keys go into the scores as projected, and ``apply``
+    is the plain cache append.  Parameters: ``head_dim``, ``row_dim`` (default ``head_dim``)."""
+
+    pairing = None
+
+    def __init__(self, spec: PartSpec, hidden_size: int) -> None:
+        super().__init__(spec, hidden_size)
+        self.head_dim = int(spec["head_dim"])
+        self.row_dim = int(spec.get("row_dim", self.head_dim))
+        if self.row_dim < self.head_dim:
+            raise ValueError("row_dim must be at least head_dim")
+        self.rotary_dim = 0
+        self._no_angles: Optional[torch.Tensor] = None
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], dtype, device) -> None:
+        self._no_angles = torch.zeros((1, 1), dtype=torch.float32, device=device)
+
+    def apply(self, ctx: StepContext, cache: LayerCache, qkv: torch.Tensor, heads: int,
+              kv_heads: int, accum: Optional[torch.Tensor] = None) -> None:
+        write = cache.owns and cache.keys is not None
+        ops.rope_append(qkv, ctx.positions, ctx.token_request, ctx.request_slot,
+                        cache.block_tables, cache.keys if write else None,
+                        cache.values if write else None, self._no_angles, self._no_angles,
+                        ctx.n_tokens, heads, kv_heads, self.row_dim, 0, 0, cache.page_size,
+                        cache.num_pages, ctx.status, accum=accum)
+
+
 register_part("position", "rotary", RotaryEncoding)
+register_part("position", "none", NoPosition)

@@ -66,12 +66,46 @@ int hx_bounded_wait_check(int polls, int arrive, int* status, int* succeeded, cu
 /* out[t, :] = table[ids[t], :] as float32 (the residual stream) */
 int hx_embed(const void* table, int dtype, const int* ids, float* out, int tokens, int hidden,
              int vocab, int* status, cudaStream_t stream);
+/* the same times a constant: out[t, :] = table[ids[t], :] * scale, the product in float32 */
+int hx_embed_scaled(const void* table, int dtype, const int* ids, float* out, int tokens,
+                    int hidden, int vocab, float scale, int* status, cudaStream_t stream);
+/* x[t, :] += y[t, :], float32 rows of `hidden` */
+int hx_add_rows(float* x, const float* y, int tokens, int hidden, cudaStream_t stream);
+/* y[r, :] = (x[r', :] - mean) / sqrt(var + eps) * weight + bias, r' = rows ? rows[r] : r, var the
+   mean of the squared deviations, float32 inside; bias may be null */
+int hx_layernorm(const float* x, const float* weight, const float* bias, void* y, int out_dtype,
+                 const int* rows, int n_rows, int hidden, float eps, cudaStream_t stream);
 /* y[r, :] = x[rows ? rows[r] : r, :] * rsqrt(mean(x^2) + eps) * weight, float32 inside */
 int hx_rmsnorm(const float* x, const float* weight, void* y, int out_dtype, const int* rows,
                int n_rows, int hidden, float eps, cudaStream_t stream);
 /* act[t, f] = silu(gate_up[t, f]) * gate_up[t, intermediate + f]; zero_input clears gate_up */
 int hx_swiglu(float* gate_up, void* act, int out_dtype, int tokens, int intermediate, int ld_in,
               int zero_input, cudaStream_t stream);
+
+/* act[t, f] = g(gate_up[t, f]) * gate_up[t, intermediate + f]; activation 0: g = silu,
+   1: g = gelu_tanh, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))) */
+int hx_gated_activation(float* gate_up, void* act, int out_dtype, int tokens, int intermediate,
+                        int ld_in, int zero_input, int activation, cudaStream_t stream);
+/* context[t, :width] *= sigmoid(gate[t, :width]); clear (may be null): float32 rows
+   [tokens, clear_width] that are zeroed afterwards */
+int hx_sigmoid_gate(void* context, int ld_context, const void* gate, int ld_gate, int dtype,
+                    int tokens, int width, float* clear, int ld_clear, int clear_width,
+                    cudaStream_t stream);
+
+/* ---- short causal filter over time + cache append --------------------------------------- */
+/* row = [q heads | k heads | v heads | passthrough], `total` columns; every q/k/v channel c is
+ * filtered along its sequence, y[t] = sum_j filter[c, j] * u[t - (taps - 1) + j], zeros before
+ * the sequence; state[slot, taps - 1, channels] carries each request's last projected values
+ * from step to step.  raw (storage dtype) or accum (float32 sums, left uncleared) is given.
+ * Queries and passthrough columns go to `out`, keys and values to their pages when
+ * write_cache, else to `out` as well. */
+int hx_short_conv_append(const void* raw, int ld_raw, const float* accum, int ld_accum, void* out,
+                         int ld_out, int dtype, const float* filter, void* state, int taps,
+                         const int* positions, const int* token_request, const int* request_slot,
+                         const int* request_start, const int* block_tables, int table_stride,
+                         void* k_cache, void* v_cache, int write_cache, int tokens, int heads,
+                         int kv_heads, int head_dim, int total, int page_size, int num_pages,
+                         int* status, cudaStream_t stream);
 
 /* ---- rotary encoding + cache append ---------------------------------------------------- */
 /* qkv row = [q heads | k heads | v heads]; pairing 0: pairs (2p, 2p+1), 1: (p, p + rotary/2).
@@ -126,6 +160,16 @@ int hx_paged_attention(const void* q, int ldq, const void* k_cache, const void* 
                        float* partial, int* arrivals, int tokens, int heads, int kv_heads,
                        int head_dim, int page_size, int num_pages, int window, float scale,
                        int split_keys, int max_splits, int* status, cudaStream_t stream);
+/* the same with kept first keys: the query at position p sees key j <= p when p - j < window or
+   j < keep_first */
+int hx_paged_attention_kept(const void* q, int ldq, const void* k_cache, const void* v_cache,
+                            int dtype, const int* positions, const int* token_request,
+                            const int* request_table_row, const int* block_tables,
+                            int table_stride, const int* request_start, int skip_query_len,
+                            void* out, int ldo, float* partial, int* arrivals, int tokens,
+                            int heads, int kv_heads, int head_dim, int page_size, int num_pages,
+                            int window, int keep_first, float scale, int split_keys,
+                            int max_splits, int* status, cudaStream_t stream);
 /* the same with scratch built into the library: see hx_no_alloc.h beside the sources */
 int hx_paged_attention_no_alloc(const void* q, int ldq, const void* k_cache, const void* v_cache,
                                 int dtype, const int* positions, const int* token_request,
