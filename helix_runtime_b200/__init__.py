@@ -10,7 +10,7 @@ model folder (``config.json`` + safetensors) to generated tokens:
 """
 from . import models  # noqa: F401  (registers the architecture and the parts)
 from .models import register_arrangement
-from .config import (ConfigError, LlamaConfig, ModelSpec, PartSpec, load_config,
+from .config import (ConfigError, LlamaConfig, ModelSpec, PartSpec, RekasunConfig, load_config,
                      register_architecture)
 from .engine import (Engine, EngineConfig, GenerationResult, StepEntry, StepError, StepFunction,
                      load_model, random_model, write_random_model)
@@ -21,7 +21,7 @@ __version__ = "0.1.0"
 
 __all__ = [
     "ConfigError", "Engine", "EngineConfig", "GenerationResult", "LlamaConfig", "ModelSpec",
-    "PartSpec", "StepEntry", "StepError", "StepFunction", "WeightError", "load_config",
+    "PartSpec", "RekasunConfig", "StepEntry", "StepError", "StepFunction", "WeightError", "load_config",
     "load_model", "random_model", "register_architecture", "register_arrangement",
     "register_part",
     "write_random_model",

@@ -51,6 +51,8 @@ struct PrefillArgs {
   float scale;
   int min_query_len;
   int* status;
+  int window;       // 0: every earlier key; else the query at p sees key j <= p with p - j < window
+  int keep_first;   // ... or j < keep_first (used with a window only)
 };
 
 constexpr int RING = 2;                         // key/value tiles in flight per CTA
@@ -117,7 +119,15 @@ __global__ __launch_bounds__(THREADS, D <= 128 ? 3 : 1) void prefill_attention_k
   const int row0 = tile_in_request * BLOCK_M;                 // first query row of the tile
   const int rows_here = min(BLOCK_M, q_len - row0);
   const int last_key = context + row0 + rows_here - 1;        // last key any row here sees
-  const int n_tiles = last_key / BLOCK_N + 1;
+  // With a window the CTA walks the tiles that hold kept first keys, then the tiles from the
+  // one that holds the first key its FIRST row sees through the window; `n_tiles` counts
+  // both runs and tile_at(i) is the i-th of them.  Keys from keep_first up to first_needed
+  // are seen by no row of the CTA: their pages may have been given back and are not read.
+  const int first_needed = a.window > 0 ? max(0, context + row0 - a.window + 1) : 0;
+  const int window_tile0 = first_needed / BLOCK_N;
+  const int kept_tiles = a.window > 0 ? min((a.keep_first + BLOCK_N - 1) / BLOCK_N, window_tile0) : 0;
+  const int n_tiles = kept_tiles + last_key / BLOCK_N + 1 - window_tile0;
+  auto tile_at = [&](int i) { return i < kept_tiles ? i : window_tile0 + (i - kept_tiles); };
   const int* table = a.block_tables +
                      static_cast<size_t>(a.request_table_row[request]) * a.table_stride;
   const int page_size = a.page_size;
@@ -133,8 +143,9 @@ __global__ __launch_bounds__(THREADS, D <= 128 ? 3 : 1) void prefill_attention_k
   __syncthreads();
 
   // one thread asks for the pages of a tile: two bulk copies (keys, values) per page
-  auto request_tile = [&](int tile) {
-    const int stage = tile % RING;
+  auto request_tile = [&](int turn) {
+    const int tile = tile_at(turn);
+    const int stage = turn % RING;
     const uint32_t base = hx_shared_address(smem) + stage * 2 * kHalfBytes;
     int pages[8];
     uint32_t expected = 0;
@@ -143,7 +154,10 @@ __global__ __launch_bounds__(THREADS, D <= 128 ? 3 : 1) void prefill_attention_k
     for (int p = 0; p < 8; ++p) {
       pages[p] = -1;
       const int index = tile * pages_per_tile + p;
-      if (p < pages_per_tile && index <= last_page) {
+      // a page that holds no kept key and ends before the first key needed is not read
+      const bool wanted = index * page_size < a.keep_first ||
+                          (index + 1) * page_size > first_needed;
+      if (p < pages_per_tile && index <= last_page && wanted) {
         const int page = table[index];
         if (page >= 0 && page < a.num_pages) {
           pages[p] = page;
@@ -216,10 +230,11 @@ __global__ __launch_bounds__(THREADS, D <= 128 ? 3 : 1) void prefill_attention_k
   const int q_pos0 = context + row0 + warp_row + (lane >> 2);   // position of the first row
   const int q_pos1 = q_pos0 + 8;
 
-  for (int tile = 0; tile < n_tiles; ++tile) {
-    const int stage = tile % RING;
+  for (int turn = 0; turn < n_tiles; ++turn) {
+    const int tile = tile_at(turn);
+    const int stage = turn % RING;
     bool arrived = true;
-    if (lane == 0) arrived = tile_wait(&full_bar[stage], static_cast<uint32_t>(tile / RING) & 1u);
+    if (lane == 0) arrived = tile_wait(&full_bar[stage], static_cast<uint32_t>(turn / RING) & 1u);
     arrived = __shfl_sync(0xffffffffu, arrived ? 1 : 0, 0) != 0;
     if (!arrived) {
       if (lane == 0 && a.status != nullptr) atomicOr(a.status, HX_FLAG_WAIT_TIMEOUT);
@@ -231,12 +246,18 @@ __global__ __launch_bounds__(THREADS, D <= 128 ? 3 : 1) void prefill_attention_k
     // Behind the last key the tile holds whatever the pages (or an earlier tile) left there.
     // Scores of such keys are masked by selection, but a value of NaN would survive a zero
     // probability, so those value rows are cleared; likewise everything of an unreadable tile.
+    // The same goes for keys between the kept ones and the first key needed: no row sees
+    // them and their pages were not read.
     const int first_stale = tile_state[stage] ? 0 : last_key + 1 - tile * BLOCK_N;
-    if (first_stale < BLOCK_N) {
+    const int unseen_from = max(a.keep_first, 0) - tile * BLOCK_N;     // tile-relative, may be < 0
+    const int unseen_to = first_needed - tile * BLOCK_N;               // exclusive
+    const bool has_unseen = a.window > 0 && unseen_to > 0 && unseen_from < BLOCK_N &&
+                            unseen_from < unseen_to;
+    if (first_stale < BLOCK_N || has_unseen) {
       for (int index = tid; index < BLOCK_N * (D / 8); index += THREADS) {
         const int key = index / (D / 8);
         const int piece = index - key * (D / 8);
-        if (key >= first_stale) {
+        if (key >= first_stale || (has_unseen && key >= unseen_from && key < unseen_to)) {
           const uint32_t address = v_base + piece_offset(key, piece, page_size, page_bytes);
           asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(address), "r"(0u) : "memory");
         }
@@ -263,7 +284,7 @@ __global__ __launch_bounds__(THREADS, D <= 128 ? 3 : 1) void prefill_attention_k
 
     // ---- scale, causal mask, running maximum
     const int key0 = tile * BLOCK_N + 2 * (lane & 3);
-    const bool needs_mask = tile * BLOCK_N + BLOCK_N - 1 > context + row0 + warp_row;
+    const bool needs_mask = a.window > 0 || tile * BLOCK_N + BLOCK_N - 1 > context + row0 + warp_row;
     float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int n = 0; n < BLOCK_N / 8; ++n) {
@@ -273,7 +294,9 @@ __global__ __launch_bounds__(THREADS, D <= 128 ? 3 : 1) void prefill_attention_k
         if (needs_mask) {
           const int key = key0 + n * 8 + (e & 1);
           const int q_pos = (e & 2) ? q_pos1 : q_pos0;
-          if (key > q_pos) value = -INFINITY;
+          if (key > q_pos ||
+              (a.window > 0 && q_pos - key >= a.window && key >= a.keep_first))
+            value = -INFINITY;
         }
         s[n][e] = value;
         tile_max[e >> 1] = fmaxf(tile_max[e >> 1], value);
@@ -298,6 +321,8 @@ __global__ __launch_bounds__(THREADS, D <= 128 ? 3 : 1) void prefill_attention_k
       o_acc[n][3] *= correction[1];
     }
 
+    const float exp_base[2] = {row_max[0] == -INFINITY ? 0.0f : row_max[0],
+                               row_max[1] == -INFINITY ? 0.0f : row_max[1]};
     // ---- P = exp(S - max), O += P V with P = hi + lo in bfloat16
 #pragma unroll
     for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
@@ -306,7 +331,8 @@ __global__ __launch_bounds__(THREADS, D <= 128 ? 3 : 1) void prefill_attention_k
       for (int half = 0; half < 2; ++half)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float value = __expf(s[kk * 2 + half][e] - row_max[e >> 1]);
+          // (a row whose keys so far were all outside its window has no maximum yet)
+          const float value = __expf(s[kk * 2 + half][e] - exp_base[e >> 1]);
           p[half][e] = value;
           row_sum[e >> 1] += value;
         }
@@ -327,9 +353,9 @@ __global__ __launch_bounds__(THREADS, D <= 128 ? 3 : 1) void prefill_attention_k
       }
     }
     __syncthreads();      // every warp is done with this stage before it is refilled
-    if (tid == 0 && tile + RING < n_tiles) {
+    if (tid == 0 && turn + RING < n_tiles) {
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      request_tile(tile + RING);
+      request_tile(turn + RING);
     }
   }
 
@@ -384,13 +410,17 @@ HX_API int hx_prefill_attention_supports(int head_dim, int page_size) {
 // Attention of every request that brings at least `min_query_len` tokens to this step.
 // `tile_bound` is an upper bound of the number of 64-row query tiles over those requests
 // (tokens / 64 + requests is always enough).
-HX_API int hx_prefill_attention(const void* q, int ldq, const void* k_cache, const void* v_cache,
-                                const int* request_start, const int* request_context,
-                                const int* request_table_row, const int* block_tables,
-                                int table_stride, void* out, int ldo, int requests, int tile_bound,
-                                int heads, int kv_heads, int head_dim, int page_size,
-                                int num_pages, float scale, int min_query_len, int* status,
-                                cudaStream_t stream) {
+// window > 0: the query at position p sees key j <= p when p - j < window or j < keep_first.
+HX_API int hx_prefill_attention_windowed(const void* q, int ldq, const void* k_cache,
+                                         const void* v_cache, const int* request_start,
+                                         const int* request_context, const int* request_table_row,
+                                         const int* block_tables, int table_stride, void* out,
+                                         int ldo, int requests, int tile_bound, int heads,
+                                         int kv_heads, int head_dim, int page_size, int num_pages,
+                                         float scale, int min_query_len, int window,
+                                         int keep_first, int* status, cudaStream_t stream) {
+  HX_REQUIRE(window >= 0 && keep_first >= 0, "hx_prefill_attention: bad window");
+  if (window == 0) keep_first = 0;
   HX_REQUIRE(hx_prefill_attention_supports(head_dim, page_size),
              "hx_prefill_attention: head_dim %d with pages of %d is not supported (head sizes in "
              "steps of 16 up to 128 and of 32 up to 256, pages of 8, 16, 32 or 64)", head_dim, page_size);
@@ -409,7 +439,8 @@ HX_API int hx_prefill_attention(const void* q, int ldq, const void* k_cache, con
                 static_cast<const __nv_bfloat16*>(k_cache),
                 static_cast<const __nv_bfloat16*>(v_cache), request_start, request_context,
                 request_table_row, block_tables, table_stride, static_cast<__nv_bfloat16*>(out),
-                ldo, requests, heads, kv_heads, page_size, num_pages, scale, min_query_len, status};
+                ldo, requests, heads, kv_heads, page_size, num_pages, scale, min_query_len, status,
+                window, keep_first};
   int rc = HX_ERR_UNSUPPORTED;
   switch (head_dim) {
     case 16: rc = launch<16>(a, tile_bound, stream); break;
@@ -428,4 +459,17 @@ HX_API int hx_prefill_attention(const void* q, int ldq, const void* k_cache, con
   if (rc != HX_OK) return rc;
   HX_CHECK_LAUNCH("hx_prefill_attention");
   return HX_OK;
+}
+
+HX_API int hx_prefill_attention(const void* q, int ldq, const void* k_cache, const void* v_cache,
+                                const int* request_start, const int* request_context,
+                                const int* request_table_row, const int* block_tables,
+                                int table_stride, void* out, int ldo, int requests, int tile_bound,
+                                int heads, int kv_heads, int head_dim, int page_size,
+                                int num_pages, float scale, int min_query_len, int* status,
+                                cudaStream_t stream) {
+  return hx_prefill_attention_windowed(q, ldq, k_cache, v_cache, request_start, request_context,
+                                       request_table_row, block_tables, table_stride, out, ldo,
+                                       requests, tile_bound, heads, kv_heads, head_dim, page_size,
+                                       num_pages, scale, min_query_len, 0, 0, status, stream);
 }

@@ -100,6 +100,11 @@ def _declare(library: ctypes.CDLL) -> None:
     library.hx_prefill_attention.restype = _c_int
     library.hx_prefill_attention_supports.argtypes = [_c_int, _c_int]
     library.hx_prefill_attention_supports.restype = _c_int
+    library.hx_prefill_attention_windowed.argtypes = [
+        _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int,
+        _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int,
+        _c_ptr, _c_ptr]
+    library.hx_prefill_attention_windowed.restype = _c_int
     library.hx_prefill_attention_tc.argtypes = library.hx_prefill_attention.argtypes
     library.hx_prefill_attention_tc.restype = _c_int
     library.hx_prefill_attention_tc_supports.argtypes = [_c_int, _c_int]
@@ -496,7 +501,8 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
                       kv_heads: int, head_dim: int, page_size: int, num_pages: int, scale: float,
                       min_query_len: int, status: torch.Tensor,
                       tensor_memory: Optional[bool] = None,
-                      query_lengths: Optional[Sequence[int]] = None) -> None:
+                      query_lengths: Optional[Sequence[int]] = None, window: int = 0,
+                      keep_first: int = 0) -> None:
     """Tensor-core attention (bfloat16) of every request that brings at least
     ``min_query_len`` tokens; ``tile_bound`` bounds the number of query tiles of 64 tokens
     (the tensor-memory kernel, whose tiles hold 256 tokens, needs no more).  A CTA that finds
@@ -505,25 +511,33 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     grid is exactly the tiles there are.
     ``tensor_memory``: take the tcgen05 kernel (scores, probabilities and output in tensor
     memory; pages of at least 16 keys) or the ``mma.sync`` kernel; default: tcgen05 where it
-    applies."""
+    applies.  ``window`` > 0 (the query at position p sees key j <= p when p - j < window or
+    j < ``keep_first``) runs on the ``mma.sync`` kernel, which skips the tiles no row sees."""
     _need(q, torch.bfloat16, "q")
     _need(k_cache, torch.bfloat16, "k_cache")
     _need(out, torch.bfloat16, "out")
+    if window:
+        if tensor_memory:
+            raise KernelError("the tcgen05 prompt attention has no window")
+        tensor_memory = False
     if tensor_memory is None:
         tensor_memory = prefill_attention_tc_supports(head_dim, page_size)
-    entry = lib().hx_prefill_attention_tc if tensor_memory else lib().hx_prefill_attention
     if query_lengths is not None:
         rows = PREFILL_TILE_ROWS_TC if tensor_memory else PREFILL_TILE_ROWS
         tile_bound = sum(-(-length // rows) for length in query_lengths
                          if length >= min_query_len)
         if tile_bound == 0:
             return
-    _check(entry(
+    arguments = (
         q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), request_start.data_ptr(),
         request_context.data_ptr(), request_table_row.data_ptr(), block_tables.data_ptr(),
         block_tables.stride(0), out.data_ptr(), out.stride(0), requests, tile_bound, heads,
-        kv_heads, head_dim, page_size, num_pages, float(scale), min_query_len, _ptr(status),
-        _stream()))
+        kv_heads, head_dim, page_size, num_pages, float(scale), min_query_len)
+    if tensor_memory:
+        _check(lib().hx_prefill_attention_tc(*arguments, _ptr(status), _stream()))
+    else:
+        _check(lib().hx_prefill_attention_windowed(*arguments, int(window), int(keep_first),
+                                                   _ptr(status), _stream()))
 
 
 def argmax(logits: torch.Tensor, tokens_out: torch.Tensor, status: Optional[torch.Tensor]) -> None:

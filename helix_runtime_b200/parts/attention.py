@@ -280,10 +280,11 @@ class PagedAttention(Mixer):
 
         window = cache.window or 0
         kept = self.keep_first if window else 0
-        # prompt portions of at least TENSOR_CORE_MIN_QUERY tokens go to the tensor-core
-        # kernel (bfloat16, no window, head sizes it has); the rest, decode tokens above all,
-        # to the CUDA-core kernel.  A step may need both.
-        tensor_cores = (ctx.dtype == torch.bfloat16 and not window
+        # prompt portions of at least TENSOR_CORE_MIN_QUERY tokens go to a tensor-core
+        # kernel (bfloat16, head sizes it has; with a window the ``mma.sync`` one); the rest,
+        # decode tokens above all, to the streaming or the CUDA-core kernel.  A step may need
+        # both.
+        tensor_cores = (ctx.dtype == torch.bfloat16
                         and ctx.max_query_len >= TENSOR_CORE_MIN_QUERY
                         and ops.prefill_attention_supports(self.row_dim, cache.page_size))
         if tensor_cores:
@@ -292,7 +293,8 @@ class PagedAttention(Mixer):
                                   context, ctx.n_requests, n // 64 + ctx.n_requests, self.heads,
                                   self.kv_heads, self.row_dim, cache.page_size, cache.num_pages,
                                   self.scale, TENSOR_CORE_MIN_QUERY, ctx.status,
-                                  query_lengths=ctx.host_query_lengths)
+                                  query_lengths=ctx.host_query_lengths, window=window,
+                                  keep_first=kept)
         if not tensor_cores or ctx.min_query_len < TENSOR_CORE_MIN_QUERY:
             longest = ctx.max_context_len if not window else \
                 min(ctx.max_context_len, window + kept)

@@ -1,0 +1,172 @@
+"""The Rekasun decoder through the engine's own model, cache manager and step function,
+against the plain implementation: every way of cutting the same requests into steps gives
+the plain logits at every position.  Pools are small, so pages and state slots are used again
+(free pages are filled with NaN); windows give pages back while their kept first pages stay.
+"""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+import plain_rekasun
+import traces
+from conftest import random_tokens
+from engine_harness import Harness, assert_close
+from rekasun_configs import CONFIGS, PAGE_SIZE, make_folder
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"mixed": (1, 2, 9, 33, 90), "plain": (3, 17, 40, 75), "fast": (5, 70, 150, 310)}
+CASES = [("mixed", "float32"), ("plain", "float32"), ("fast", "float32"),
+         ("mixed", "bfloat16"), ("plain", "bfloat16"), ("fast", "bfloat16")]
+# float32: double against float32 sums.  bfloat16: the plain implementation rounds where the
+# engine stores; what is left are activations that fall on the other side of a rounding
+# boundary, which sharp attention carries into logits of spread one.
+TOLERANCE = {"float32": dict(atol=3e-4, rtol=3e-4), "bfloat16": dict(atol=6e-2, rtol=3e-2)}
+
+
+def make_requests(name: str, extra: int = 0):
+    vocab = CONFIGS[name]["vocab"]
+    return {f"r{index}": random_tokens(vocab, length + extra, seed=77 * len(name) + index)
+            for index, length in enumerate(LENGTHS[name])}
+
+
+@pytest.fixture(scope="module")
+def models(model_root):
+    cache = {}
+
+    def get(name: str, dtype: str):
+        if (name, dtype) not in cache:
+            folder = make_folder(model_root, name, dtype)
+            cache[(name, dtype)] = (folder, plain_rekasun.PlainRekasun(folder, precision=dtype))
+        return cache[(name, dtype)]
+    return get
+
+
+@pytest.fixture(scope="module")
+def expectations(models):
+    cache = {}
+
+    def get(name: str, dtype: str, extra: int = 0):
+        if (name, dtype, extra) not in cache:
+            plain = models(name, dtype)[1]
+            cache[(name, dtype, extra)] = {request: plain.logits(tokens)
+                                           for request, tokens in make_requests(name, extra).items()}
+        return cache[(name, dtype, extra)]
+    return get
+
+
+def replay(harness: Harness, steps, expected, dtype: str, what: str):
+    positions = {}
+    for step in steps:
+        rows = traces.labels(step, positions)
+        out = harness.run([(e["id"], e["tokens"], e["want"]) for e in step["entries"]])
+        for name in step["end"]:
+            harness.end(name)
+        if rows:
+            want = np.stack([expected[name][position] for name, position in rows])
+            assert_close(out, want, f"{what} step {step['step']} rows {rows[:4]}...",
+                         **TOLERANCE[dtype])
+        harness.cache.check()
+    assert not harness.cache.live_requests()
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_whole_requests(name, dtype, models, expectations):
+    harness = Harness(models(name, dtype)[0], dtype, PAGE_SIZE[name], num_pages=48)
+    replay(harness, traces.whole(make_requests(name)), expectations(name, dtype), dtype,
+           f"whole {name} {dtype}")
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_residual_stream_after_every_layer_run(name, dtype, models):
+    folder, plain = models(name, dtype)
+    harness = Harness(folder, dtype, PAGE_SIZE[name], num_pages=48)
+    tokens = make_requests(name)["r3"]
+    seen = []
+    harness.model.after_entry = lambda index, rows: seen.append(rows.float().cpu().numpy().copy())
+    harness.whole("a", tokens)
+    states = plain.hidden_states(tokens)
+    assert len(seen) == len(states)
+    for index, (got, want) in enumerate(zip(seen, states)):
+        spread = float(np.abs(want).max())
+        tolerance = 2e-5 * spread if dtype == "float32" else 3e-2 * spread
+        assert_close(got, want.astype(np.float32), f"{name} {dtype} layer run {index}",
+                     atol=tolerance, rtol=0.0)
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_tail_decoded_one_by_one(name, dtype, models, expectations):
+    # 60 decoded tokens: every window of these models passes over decoded tokens
+    harness = Harness(models(name, dtype)[0], dtype, PAGE_SIZE[name], num_pages=48)
+    replay(harness, traces.tail_decoded(make_requests(name, extra=30), tail=60),
+           expectations(name, dtype, 30), dtype, f"tail {name} {dtype}")
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_portions_of_changing_size(name, dtype, models, expectations):
+    harness = Harness(models(name, dtype)[0], dtype, PAGE_SIZE[name], num_pages=48)
+    replay(harness, traces.chunked(make_requests(name, extra=30)), expectations(name, dtype, 30),
+           dtype, f"portions {name} {dtype}")
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+@pytest.mark.parametrize("seed", [0, 1])
+def test_mixed_batches_over_a_small_pool(name, dtype, seed, models, expectations):
+    requests = make_requests(name, extra=30)
+    steps = traces.mixed(requests, max_live=3, seed=seed)
+    page = PAGE_SIZE[name]
+    pages = -(-traces.live_token_need(steps, round_to=page) // page)
+    harness = Harness(models(name, dtype)[0], dtype, page, num_pages=pages, max_requests=3)
+    replay(harness, steps, expectations(name, dtype, 30), dtype, f"mixed {name} {dtype}")
+    stats = harness.cache.stats()
+    assert all(group["reuses"] > 0 for group in stats["groups"]), "no page was used again"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_windowed_layer_needs_no_more_pages_than_its_window(dtype, models):
+    """A long request over a pool that could never hold all of it: the windowed groups give
+    pages back as the window passes them, the kept first pages stay, and the logits at the
+    end are those of the whole sequence."""
+    name = "mixed"
+    folder, plain = models(name, dtype)
+    tokens = random_tokens(CONFIGS[name]["vocab"], 200, seed=5)
+    # the widest layer keeps 20 first keys (3 pages of 8) and sees 40 (6 pages) + the portion
+    harness = Harness(folder, dtype, PAGE_SIZE[name], num_pages=14, max_requests=1)
+    expected = plain.logits(tokens)
+    cursor = 0
+    for size in [13, 8, 8, 3, 11] * 10:
+        size = min(size, len(tokens) - cursor)
+        if size == 0:
+            break
+        out = harness.run([("long", tokens[cursor:cursor + size], range(size))])
+        assert_close(out, expected[cursor:cursor + size], f"positions from {cursor}",
+                     **TOLERANCE[dtype])
+        cursor += size
+        harness.cache.check()
+    assert cursor == len(tokens)
+    harness.end("long")
+
+
+@pytest.mark.parametrize("name,dtype", [("mixed", "float32"), ("fast", "bfloat16")])
+def test_greedy_generation_through_the_engine(name, dtype, models):
+    """``Engine.generate``: scheduler, continuous batching, CUDA graphs and sampling, several
+    requests at once.  Each generated token must be (within rounding) the best token of the
+    plain logits for the sequence so far."""
+    from helix_runtime_b200 import Engine
+    folder, plain = models(name, dtype)
+    vocab = CONFIGS[name]["vocab"]
+    prompts = [random_tokens(vocab, length, seed=300 + length) for length in (3, 25, 61)]
+    engine = Engine.from_pretrained(folder, dtype=dtype, page_size=PAGE_SIZE[name], num_pages=64,
+                                    max_running_requests=3, max_tokens_per_iteration=64,
+                                    max_prefill_chunk=24, poison_free_pages=True)
+    results = engine.generate(prompts, max_new_tokens=24)
+    slack = 1e-3 if dtype == "float32" else 0.12
+    for prompt, result in zip(prompts, results):
+        tokens = list(prompt)
+        assert len(result.generated_tokens) == 24
+        for token in result.generated_tokens:
+            logits = plain.logits(tokens)[-1]
+            assert logits[token] >= logits.max() - slack, \
+                f"token {token} at position {len(tokens)} is not the plain model's choice"
+            tokens.append(token)
