@@ -160,12 +160,12 @@ def serving_workload(options, model, config, rng) -> int:
     requests = options.serving
     work = WORKLOADS[options.shape]
     low, high = work["prompt_range"]
-    high = min(high, config.max_position_embeddings - work["new_tokens"])
-    shared = [int(t) for t in rng.integers(0, config.vocab_size, work["shared_prefix"])]
+    high = min(high, model.max_positions - work["new_tokens"])
+    shared = [int(t) for t in rng.integers(0, model.vocab_size, work["shared_prefix"])]
     prompts = []
     for _ in range(requests):
         length = max(int(rng.integers(low, high + 1)), len(shared) + 1)
-        prompts.append(shared + [int(t) for t in rng.integers(0, config.vocab_size,
+        prompts.append(shared + [int(t) for t in rng.integers(0, model.vocab_size,
                                                               length - len(shared))])
     submitted = sum(len(prompt) for prompt in prompts)
     engine = Engine(model, EngineConfig(page_size=PAGE_SIZE, max_running_requests=min(requests, 64),
@@ -223,7 +223,7 @@ def profile_region(options, model, config, fresh, rng) -> int:
     length = options.prompt_len
     batch = options.batch if options.profile == "decode" else 1
     cache, step, sampler = fresh(batch, length + 8, max(length, batch, PREFILL_TOKENS))
-    prompts = [[int(t) for t in rng.integers(0, config.vocab_size, length)] for _ in range(batch)]
+    prompts = [[int(t) for t in rng.integers(0, model.vocab_size, length)] for _ in range(batch)]
     for index in range(batch):
         cache.admit(index)
     if options.profile == "prefill":
@@ -272,7 +272,7 @@ def timeline_region(options, model, config, fresh, rng) -> int:
     length, batch = options.prompt_len, options.batch
     if options.timeline == "prefill":
         cache, step, _ = fresh(1, length + 8, length)
-        prompt = [int(t) for t in rng.integers(0, config.vocab_size, length)]
+        prompt = [int(t) for t in rng.integers(0, model.vocab_size, length)]
 
         def run():
             cache.admit(0)
@@ -286,7 +286,7 @@ def timeline_region(options, model, config, fresh, rng) -> int:
         contexts = (1536, 1024, 512, 0)
         cache, step, _ = fresh(batch + len(contexts), max(length, max(contexts) + 512) + 8,
                                PREFILL_TOKENS + batch)
-        draw = lambda count: [int(t) for t in rng.integers(0, config.vocab_size, count)]
+        draw = lambda count: [int(t) for t in rng.integers(0, model.vocab_size, count)]
         for request in range(batch + len(contexts)):
             cache.admit(request)
         for request in range(batch):                       # bring the decode requests to length
@@ -308,16 +308,16 @@ def timeline_region(options, model, config, fresh, rng) -> int:
         # the first requests decode while the prompts of the last are still being fed: every
         # request gets tokens enough to be decoding still when the recorded steps are over
         feeding = -(-batch * length // PREFILL_TOKENS) + batch
-        budget = min(feeding + 48, config.max_position_embeddings - length)
+        budget = min(feeding + 48, model.max_positions - length)
         if budget < feeding + 17:
             raise SystemExit(f"bench.py: {batch} prompts of {length} tokens leave no room to "
-                             f"decode within {config.max_position_embeddings} positions")
+                             f"decode within {model.max_positions} positions")
         engine = Engine(model, EngineConfig(
             page_size=PAGE_SIZE, max_running_requests=batch,
             max_tokens_per_iteration=PREFILL_TOKENS,
             num_pages=batch * -(-(length + budget) // PAGE_SIZE) + 8))
         for _ in range(batch):
-            engine.submit([int(t) for t in rng.integers(0, config.vocab_size, length)],
+            engine.submit([int(t) for t in rng.integers(0, model.vocab_size, length)],
                           max_new_tokens=budget)
         for _ in range(4 * feeding + 16):
             if all(engine.request(r).state.value == "decoding" for r in range(batch)):
@@ -348,11 +348,133 @@ def timeline_region(options, model, config, fresh, rng) -> int:
         row[2] += max(0.0, end - (begin if latest_end is None else max(begin, latest_end)))
         latest_end = end if latest_end is None else max(latest_end, end)
     span = events[-1].time_range.end - events[0].time_range.start
-    print(f"{options.timeline}: {config.num_hidden_layers} layers, batch {batch}, "
+    print(f"{options.timeline}: {options.layers} layers, batch {batch}, "
           f"{length} tokens of context or prompt; {steps} step(s) span {span:.1f} us")
     print(f"{'launches':>8} {'mean us':>9} {'exclusive us':>12} {'sum excl us':>12}  kernel")
     for name, (count, total, exclusive) in table.items():
         print(f"{count:8d} {total / count:9.1f} {exclusive / count:12.1f} {exclusive:12.1f}  {name}")
+    return 0
+
+
+def rekasun_config(shape: dict, options):
+    """The Rekasun design with the layer sizes of a Llama shape: the same width, heads, head
+    size, feed-forward and vocabulary; every layer alike, no repeated stretch."""
+    import math
+
+    from helix_runtime_b200.config.rekasun import (AttentionMixerConfig, DenseMlpConfig,
+                                                   RekasunConfig, RekasunLayerConfig)
+    heads, dim = shape["num_attention_heads"], shape["head_dim"]
+    mixer = AttentionMixerConfig(heads=heads, kv_heads=options.kv_heads or heads, dim=dim, vdim=dim,
+                                 scale=1.0 / math.sqrt(dim), conv=options.taps,
+                                 window=options.window, keep_first=options.keep_first)
+    layer = RekasunLayerConfig("attention", mixer, DenseMlpConfig(shape["intermediate_size"]))
+    return RekasunConfig(vocab=shape["vocab_size"], width=shape["hidden_size"], embedding_scale=1.0,
+                         norm_eps=shape["rms_norm_eps"],
+                         layers=tuple(layer for _ in range(shape["num_hidden_layers"])),
+                         max_positions=shape["max_position_embeddings"])
+
+
+def compare_designs(options, peaks, device) -> int:
+    """``--compare``: the Rekasun design beside the Llama design at equal layer sizes, a few
+    layers (``--layers``, default 4) of every benchmark shape, random weights, bfloat16.
+    Prefill: one prompt of 2,048 tokens through the step function, CUDA events over five
+    repeats.  Decode: ``--batch`` (default 8) and 64 requests at a context of 1,536 through
+    ``Engine.run_iteration`` (scheduler, CUDA graphs, sampling), ``--steps`` iterations timed
+    with CUDA events after ``--warmup``.  Every step streams more weights than the L2 holds."""
+    import numpy as np
+    import torch
+
+    from helix_runtime_b200 import Engine, EngineConfig, LlamaConfig, random_model
+    from helix_runtime_b200.cache.manager import CacheManager
+    from helix_runtime_b200.engine.step import StepEntry, StepFunction
+
+    layers = options.layers or 4
+    context = 1536
+    steps, warmup = min(options.steps, 64), max(options.warmup, 3)
+    rng = np.random.default_rng(0)
+
+    def events_ms(fn, count):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(count):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / count
+
+    def measure(model):
+        kv, state = model.cache_needs()
+        cache = CacheManager(kv, state, PAGE_SIZE, PREFILL_TOKENS // PAGE_SIZE + 8, 1,
+                             model.max_positions, model.dtype, device)
+        step = StepFunction(model, cache, max_tokens=PREFILL_TOKENS, max_requests=1)
+        prompt = [int(t) for t in rng.integers(0, model.vocab_size, PREFILL_TOKENS)]
+
+        def prefill_once():
+            cache.admit("p")
+            step.run([StepEntry("p", prompt, [PREFILL_TOKENS - 1])], check_status=False)
+            cache.release("p")
+        for _ in range(3):
+            prefill_once()
+        prefill_ms = events_ms(prefill_once, 5)
+        step.raise_on_status()
+        del cache, step
+        torch.cuda.empty_cache()
+        result = {"prefill_ms": round(prefill_ms, 3),
+                  "prefill_tokens_per_s": round(PREFILL_TOKENS / prefill_ms * 1e3, 1)}
+        for batch in sorted({options.batch, 64}):
+            new_tokens = warmup + steps + 2 * batch + 16
+            engine = Engine(model, EngineConfig(
+                page_size=PAGE_SIZE, max_running_requests=batch,
+                max_tokens_per_iteration=PREFILL_TOKENS,
+                num_pages=batch * -(-(context + new_tokens) // PAGE_SIZE) + 8))
+            ids = [engine.submit([int(t) for t in rng.integers(0, model.vocab_size, context)],
+                                 max_new_tokens=new_tokens) for _ in range(batch)]
+            while any(engine.request(r).state.value != "decoding" for r in ids):
+                engine.run_iteration()
+            for _ in range(warmup):
+                engine.run_iteration()
+            ms = events_ms(engine.run_iteration, steps)
+            kernels = max(engine.graphs.kernels_per_graph.values(), default=0)
+            for request_id in ids:
+                engine.cancel(request_id)
+            engine.run_until_done()
+            step_bytes = model.weight_bytes_per_step() + batch * sum(
+                2 * need.kv_heads * need.head_dim * 2
+                * (context if need.window is None else min(context, need.window + need.keep_first))
+                for need in kv.values())
+            result[f"decode_b{batch}_ms"] = round(ms, 4)
+            result[f"decode_b{batch}_tokens_per_s"] = round(batch / ms * 1e3, 1)
+            result[f"decode_b{batch}_hbm_frac"] = round(step_bytes / (ms / 1e3) / 1e9
+                                                        / peaks["hbm_gbs"], 4)
+            result[f"decode_b{batch}_kernels"] = int(kernels)
+            del engine
+            torch.cuda.empty_cache()
+        return result
+
+    sampler_clock = ClockSampler(os.path.join(options.log_dir or tempfile.mkdtemp(prefix="helix_bench_"),
+                                              "compare_clocks.csv"))
+    sampler_clock.start()
+    shapes = {}
+    for name in ([options.shape] if options.shape != "llama-2-7b" else list(SHAPES)):
+        shape = dict(SHAPES[name], num_hidden_layers=layers)
+        row = {"hidden": shape["hidden_size"], "heads": shape["num_attention_heads"],
+               "head_dim": shape["head_dim"], "intermediate": shape["intermediate_size"]}
+        for design, config in (("llama", LlamaConfig(**shape)),
+                               ("rekasun", rekasun_config(shape, options))):
+            model = random_model(config, seed=0, dtype="bfloat16", device=device)
+            row[design] = measure(model)
+            del model
+            torch.cuda.empty_cache()
+        shapes[name] = row
+    print(json.dumps({
+        "metric": "prefill and decode throughput, Rekasun design beside Llama design (bf16)",
+        "layers": layers, "prefill_tokens": PREFILL_TOKENS, "decode_context": context,
+        "rekasun": {"window": options.window, "keep_first": options.keep_first,
+                    "taps": options.taps, "kv_heads": options.kv_heads or "as query heads"},
+        "steps": steps, "warmup": warmup, "data": "synthetic: random weights from seed 0",
+        "shapes": shapes, "clocks": sampler_clock.stop(), "peak_source": peaks["source"],
+        "impl": "ours"}))
     return 0
 
 
@@ -379,6 +501,22 @@ def main() -> int:
     parser.add_argument("--shape", choices=tuple(SHAPES), default="llama-2-7b",
                         help="layer sizes for --serving, --profile and --timeline (the contract "
                              "line is always the Llama-2-7B shape)")
+    parser.add_argument("--design", choices=("llama", "rekasun"), default="llama",
+                        help="which decoder the layers of --shape are built as, for --profile "
+                             "and --timeline (the contract line is always the Llama design)")
+    parser.add_argument("--compare", action="store_true",
+                        help="prefill and decode throughput of the Rekasun design beside the "
+                             "Llama design at equal layer sizes (a few layers of each --shape), "
+                             "as one JSON line of its own")
+    parser.add_argument("--window", type=int, default=1024,
+                        help="--design rekasun / --compare: keys a position sees behind itself")
+    parser.add_argument("--keep-first", type=int, default=64,
+                        help="--design rekasun / --compare: first keys that stay visible")
+    parser.add_argument("--taps", type=int, default=3,
+                        help="--design rekasun / --compare: taps of the causal filter on q, k, v")
+    parser.add_argument("--kv-heads", type=int, default=None,
+                        help="--design rekasun / --compare: key/value heads of the Rekasun "
+                             "layers (default: as many as query heads, the Llama design's rule)")
     parser.add_argument("--cache-fraction", type=float, default=0.5,
                         help="--serving: share of the memory left after the weights that the "
                              "cache pool takes")
@@ -393,10 +531,13 @@ def main() -> int:
         return 2
     if options.warmup < 3:
         options.warmup = 3
-    special = bool(options.serving or options.profile or options.timeline)
+    special = bool(options.serving or options.profile or options.timeline or options.compare)
     if options.shape != "llama-2-7b" and not special:
         print("bench.py: the contract line is measured at the Llama-2-7B shape; --shape goes with "
-              "--serving, --profile or --timeline")
+              "--serving, --profile, --timeline or --compare")
+        return 2
+    if options.design != "llama" and not (options.profile or options.timeline):
+        print("bench.py: --design goes with --profile or --timeline (--compare runs both designs)")
         return 2
 
     import numpy as np
@@ -415,8 +556,12 @@ def main() -> int:
     shape = dict(SHAPES[options.shape])
     if options.layers is None:
         options.layers = shape["num_hidden_layers"]
+    if options.compare:
+        return compare_designs(options, peaks, device)
     shape["num_hidden_layers"] = options.layers
     config = LlamaConfig(**shape)
+    if options.design == "rekasun":
+        config = rekasun_config(shape, options)
     model = random_model(config, seed=0, dtype="bfloat16", device=device)
     rng = np.random.default_rng(0)
     out_dir = options.log_dir or tempfile.mkdtemp(prefix="helix_bench_")
@@ -426,7 +571,7 @@ def main() -> int:
     def fresh(batch: int, total_len: int, capacity: int):
         kv, state = model.cache_needs()
         pages = batch * -(-total_len // PAGE_SIZE) + 8
-        cache = CacheManager(kv, state, PAGE_SIZE, pages, batch, config.max_position_embeddings,
+        cache = CacheManager(kv, state, PAGE_SIZE, pages, batch, model.max_positions,
                              model.dtype, device)
         step = StepFunction(model, cache, max_tokens=capacity, max_requests=batch)
         sampler = Sampler(device, max(batch, 1))
@@ -464,7 +609,7 @@ def main() -> int:
         per_step, contexts = [], []
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         while len(per_step) < 3 or sum(per_step) * n_steps < MIN_TIMED_SECONDS * 1e3:
-            ids = [engine.submit([int(t) for t in rng.integers(0, config.vocab_size, prompt_len)],
+            ids = [engine.submit([int(t) for t in rng.integers(0, model.vocab_size, prompt_len)],
                                  max_new_tokens=new_tokens) for _ in range(batch)]
             while any(engine.request(r).state.value != "decoding" for r in ids):
                 engine.run_iteration()
@@ -532,7 +677,7 @@ def main() -> int:
     sampler_clock = ClockSampler(os.path.join(out_dir, "bench_clocks.csv"))
     sampler_clock.start()
     cache, step, sampler = fresh(1, PREFILL_TOKENS, PREFILL_TOKENS)
-    prompt = [int(t) for t in rng.integers(0, config.vocab_size, PREFILL_TOKENS)]
+    prompt = [int(t) for t in rng.integers(0, model.vocab_size, PREFILL_TOKENS)]
 
     def prefill_once():
         cache.admit("p")
@@ -545,7 +690,7 @@ def main() -> int:
     prefill_ms = timed(prefill_once, reps) / reps
     step.raise_on_status()
     h, i, layers, t = config.hidden_size, config.intermediate_size, options.layers, PREFILL_TOKENS
-    prefill_flops = 2.0 * t * layers * (4 * h * h + 3 * h * i) + 2.0 * h * config.vocab_size \
+    prefill_flops = 2.0 * t * layers * (4 * h * h + 3 * h * i) + 2.0 * h * model.vocab_size \
         + 2.0 * layers * t * (t + 1) * h
     prefill_rate = prefill_flops / (prefill_ms / 1e3) / 1e12
     prefill = {"value": round(t / (prefill_ms / 1e3), 1), "tokens": t, "ms": round(prefill_ms, 3),
@@ -597,10 +742,10 @@ def main() -> int:
         "config": {"model": "llama-2-7b-shape", "layers": options.layers,
                    "layers_full": SHAPE["num_hidden_layers"], "hidden": h,
                    "heads": config.num_attention_heads, "kv_heads": config.num_key_value_heads,
-                   "head_dim": config.head_dim, "intermediate": i, "vocab": config.vocab_size,
+                   "head_dim": config.head_dim, "intermediate": i, "vocab": model.vocab_size,
                    "global_batch": options.batch, "seq_len": PROMPT_LEN, "gen_len": GENERATED,
                    "timed_prompt_len": facts["prompt_len"], "timed_context_mean": round(facts["context_mean"], 1),
-                   "context": config.max_position_embeddings, "page_size": PAGE_SIZE,
+                   "context": model.max_positions, "page_size": PAGE_SIZE,
                    "parallelism": "single-gpu",
                    "l2": "each step streams >126MB of weights; no flush needed"},
         "e2e": e2e, "gpu_launches": int(kernels_per_step * steps * len(repeats_ms)),

@@ -11,11 +11,12 @@
 //
 // Two kernels share the splitting and merging:
 //
-//  * the CUDA-core kernel takes every dtype, head size, page size and window: per chunk of
+//  * the CUDA-core kernel takes every dtype, head size, page size and window (with kept first
+//    keys): per chunk of
 //    32 keys, lane j owns key j for the score and a slice of the head dimension for the
 //    weighted value sum, all in float32;
 //  * the streaming kernel (bfloat16, head sizes in steps of 16 up to 128 and of 32 up to
-//    256, pages of 8, 16 or 32 keys, no window) is what decoding runs.  The keys of a (page, head) are one contiguous block of
+//    256, pages of 8, 16 or 32 keys; windows and kept first keys too) is what decoding runs.  The keys of a (page, head) are one contiguous block of
 //    the cache and so are its values, so a 32-key chunk is fetched with a few bulk copies
 //    (cp.async.bulk counted on an mbarrier) into a ring of shared-memory slots that belongs
 //    to the warp, and both products run on the tensor cores straight out of those slots: the
@@ -374,14 +375,43 @@ __device__ __forceinline__ int row_keys(const AttentionArgs& a, int token) {
   return a.positions[token] + 1;
 }
 
+// With a window a row of `keys` keys (its own position + 1) sees the keys from
+// lo = keys - window on, and the first keep_first keys behind that.  Its chunks are the blocks
+// of KEYS keys that hold kept keys (as far as they end before the block of `lo`) followed by
+// the blocks from the one that holds `lo`: chunk c of the row is block c below `kept`, block
+// c + skip from there on.
+template <int KEYS>
+__device__ __forceinline__ void row_chunks(const AttentionArgs& a, int keys, int& n, int& kept,
+                                           int& skip) {
+  kept = 0;
+  skip = 0;
+  n = (keys + KEYS - 1) / KEYS;
+  if (a.window > 0 && keys > a.window) {
+    const int first_block = (keys - a.window) / KEYS;
+    kept = min((a.keep_first + KEYS - 1) / KEYS, first_block);
+    skip = first_block - kept;
+    n -= skip;
+  }
+}
+
+template <int KEYS>
+__device__ __forceinline__ int chunks_of(const AttentionArgs& a, int keys) {
+  int n, kept, skip;
+  row_chunks<KEYS>(a, keys, n, kept, skip);
+  return n;
+}
+
 // A place in the flat list of chunks: rows (token, head) in ascending order, the chunks of a
 // row in ascending order of their keys.
 struct ChunkCursor {
   int token, head, chunk;
   int n;                  // chunks in a row of this token
-  int keys;               // keys this token sees
+  int keys;               // the token's position + 1: the keys it sees without a window
+  int kept, skip;         // see row_chunks
   int table_row;          // row of the block table that holds the token's pages
   long long row_begin;    // flat index of the row's first chunk
+  // the block of KEYS keys that chunk `chunk` of the row is
+  __device__ __forceinline__ int block() const { return chunk < kept ? chunk : chunk + skip; }
 };
 
 template <int KEYS>
@@ -394,7 +424,7 @@ __device__ __forceinline__ void cursor_next(const AttentionArgs& a, ChunkCursor&
   do {
     ++c.token;
     c.keys = row_keys(a, c.token);
-    c.n = (c.keys + KEYS - 1) / KEYS;
+    row_chunks<KEYS>(a, c.keys, c.n, c.kept, c.skip);
   } while (c.n == 0 && c.token < a.tokens);
   if (c.token < a.tokens) {
     c.table_row = a.request_table_row[a.token_request[c.token]];
@@ -522,13 +552,13 @@ void paged_attention_stream_kernel(
   {
     first_keys = row_keys(a, lane);
     if (lane < a.tokens) first_table_row = a.request_table_row[a.token_request[lane]];
-    first_inclusive = (first_keys + KEYS - 1) / KEYS;
+    first_inclusive = chunks_of<KEYS>(a, first_keys);
     // the rest of the tokens (a step that mixes prompt portions with decode tokens brings
     // thousands): every lane adds up its own, with the loads of several rounds in flight
     int mine = first_inclusive;
 #pragma unroll 4
     for (int token = 32 + lane; token < a.tokens; token += 32)
-      mine += (row_keys(a, token) + KEYS - 1) / KEYS;
+      mine += chunks_of<KEYS>(a, row_keys(a, token));
 #pragma unroll
     for (int offset = 1; offset < 32; offset <<= 1) {
       const int other = __shfl_up_sync(0xffffffffu, first_inclusive, offset);
@@ -558,7 +588,7 @@ void paged_attention_stream_kernel(
       int keys = first_keys, inclusive = first_inclusive, table_row = first_table_row;
       if (base > 0) {
         keys = row_keys(a, base + lane);
-        inclusive = (keys + KEYS - 1) / KEYS;
+        inclusive = chunks_of<KEYS>(a, keys);
 #pragma unroll
         for (int offset = 1; offset < 32; offset <<= 1) {
           const int other = __shfl_up_sync(0xffffffffu, inclusive, offset);
@@ -570,7 +600,7 @@ void paged_attention_stream_kernel(
         const int source = __ffs(beyond) - 1;
         found = base + source;
         at.keys = __shfl_sync(0xffffffffu, keys, source);
-        at.n = (at.keys + KEYS - 1) / KEYS;
+        row_chunks<KEYS>(a, at.keys, at.n, at.kept, at.skip);
         before += __shfl_sync(0xffffffffu, inclusive, source) - at.n;
         at.table_row = base == 0 ? __shfl_sync(0xffffffffu, table_row, source)
                                  : a.request_table_row[a.token_request[found]];
@@ -611,7 +641,10 @@ void paged_attention_stream_kernel(
   // request the copies of the chunk at `ahead` into ring slot `slot`; every lane follows,
   // lane 0 issues
   auto request_chunk = [&](int slot) {
-    const int first = ahead.chunk * pages_per_chunk;
+    const int first = ahead.block() * pages_per_chunk;
+    // keys below this one are outside the row's window; their pages, unless they hold kept
+    // keys, may have been given back and are not read
+    const int first_seen = a.window > 0 ? max(0, ahead.keys - a.window) : 0;
     if (ahead.token != window_token || first < window_base || first >= window_base + 32) {
       window_token = ahead.token;
       window_base = first & ~31;
@@ -626,21 +659,25 @@ void paged_attention_stream_kernel(
     int pages[kMaxPages];
     uint32_t expected = 0;
     unsigned bits = 0u;
+    bool faulty = false;
 #pragma unroll
     for (int p = 0; p < kMaxPages; ++p) {
       pages[p] = -1;
       if (p < pages_per_chunk && (first + p) * page_size < ahead.keys) {
         const int page = __shfl_sync(0xffffffffu, window_pages, first + p - window_base);
-        if (page >= 0 && page < a.num_pages) {
+        const bool wanted = (first + p + 1) * page_size > first_seen ||
+                            (first + p) * page_size < a.keep_first;
+        if (wanted && page >= 0 && page < a.num_pages) {
           pages[p] = page;
           expected += 2 * page_bytes;
         } else {
-          bits |= 1u << p;
+          bits |= 1u << p;      // its keys are left out and its value rows cleared
+          faulty = faulty || wanted;
         }
       }
     }
     unreadable = (unreadable & ~(0xfu << (4 * slot))) | (bits << (4 * slot));
-    any_unreadable = any_unreadable || bits != 0u;
+    any_unreadable = any_unreadable || faulty;
     if (lane == 0) {
       asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
                        hx_shared_address(bar)), "r"(expected) : "memory");
@@ -667,7 +704,7 @@ void paged_attention_stream_kernel(
   // and walking over them costs a chain of loads each.)
   int requested = 0;
   for (; requested < RING && requested < run; ++requested) {
-    if ((ahead.chunk + 1) * KEYS > ahead.keys - a.tokens) break;
+    if ((ahead.block() + 1) * KEYS > ahead.keys - a.tokens) break;
     request_chunk(requested);
     if (requested + 1 < run) cursor_next<KEYS>(a, ahead);
   }
@@ -735,7 +772,10 @@ void paged_attention_stream_kernel(
     }
     const uint32_t k_half = hx_shared_address(ring + static_cast<size_t>(slot) * Config::kSlotBytes);
     const uint32_t v_half = k_half + Config::kChunkBytes;
-    const int keys_here = min(KEYS, at.keys - at.chunk * KEYS);
+    const int block_key0 = at.block() * KEYS;            // position of the chunk's first key
+    const int keys_here = min(KEYS, at.keys - block_key0);
+    // a chunk that reaches below the window's first key holds keys the row does not see
+    const int window_from = a.window > 0 ? at.keys - a.window - block_key0 : -1;
     const unsigned bad_pages = (unreadable >> (4 * slot)) & 0xfu;
 
     // Whatever lies behind the last key of the request in its last page, and pages that
@@ -778,7 +818,7 @@ void paged_attention_stream_kernel(
       score[2 * tile + 1] = s[tile][2];
     }
     float chunk_max = -INFINITY;
-    if (keys_here == KEYS && bad_pages == 0u) {
+    if (keys_here == KEYS && bad_pages == 0u && window_from <= 0) {
 #pragma unroll
       for (int j = 0; j < 2 * kTiles; ++j) {
         score[j] *= a.scale;
@@ -788,7 +828,8 @@ void paged_attention_stream_kernel(
 #pragma unroll
       for (int j = 0; j < 2 * kTiles; ++j) {
         const int key = group + 8 * j;
-        const bool visible = key < keys_here && !((bad_pages >> (key / page_size)) & 1u);
+        const bool visible = key < keys_here && !((bad_pages >> (key / page_size)) & 1u) &&
+                             (key >= window_from || block_key0 + key < a.keep_first);
         score[j] = visible ? score[j] * a.scale : -INFINITY;
         chunk_max = fmaxf(chunk_max, score[j]);
       }
@@ -938,7 +979,7 @@ int launch_stream(const AttentionArgs& a, cudaStream_t stream) {
 
 bool stream_kernel_applies(const AttentionArgs& a, int dtype) {
   return dtype == HX_BF16 && a.head_dim >= 16 && a.head_dim <= 256 &&
-         a.head_dim % (a.head_dim <= 128 ? 16 : 32) == 0 && a.window == 0 &&
+         a.head_dim % (a.head_dim <= 128 ? 16 : 32) == 0 &&
          (a.page_size == 8 || a.page_size == 16 || a.page_size == 32);
 }
 
@@ -1004,7 +1045,7 @@ HX_API long long hx_paged_attention_scratch_floats(int tokens, int heads, int he
 }
 
 // The same for a caller that says which case it has: the streaming kernel (bfloat16, head
-// sizes in steps of 16 up to 128 and of 32 up to 256, pages of 8 to 32 keys, no window) needs its two parts per warp only,
+// sizes in steps of 16 up to 128 and of 32 up to 256, pages of 8 to 32 keys) needs its two parts per warp only,
 // whatever the number of tokens and splits.
 HX_API long long hx_paged_attention_scratch_floats_for(int dtype, int tokens, int heads,
                                                        int head_dim, int page_size, int window,

@@ -284,7 +284,11 @@ __global__ __launch_bounds__(THREADS, D <= 128 ? 3 : 1) void prefill_attention_k
 
     // ---- scale, causal mask, running maximum
     const int key0 = tile * BLOCK_N + 2 * (lane & 3);
-    const bool needs_mask = a.window > 0 || tile * BLOCK_N + BLOCK_N - 1 > context + row0 + warp_row;
+    // a tile needs the mask when it reaches beyond the first row's own key, or (window) when
+    // its first key lies outside the window of this warp's last row
+    const bool needs_mask = tile * BLOCK_N + BLOCK_N - 1 > context + row0 + warp_row ||
+                            (a.window > 0 &&
+                             context + row0 + warp_row + 15 - tile * BLOCK_N >= a.window);
     float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int n = 0; n < BLOCK_N / 8; ++n) {

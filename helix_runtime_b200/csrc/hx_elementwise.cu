@@ -340,6 +340,78 @@ __global__ __launch_bounds__(256) void layernorm_kernel(
   }
 }
 
+// The same for widths that are a multiple of four and fit in registers (to 4 * 256 *
+// LN_VECTORS): float4 loads, the row read once, weight and bias (which no earlier kernel
+// writes) fetched before the dependency wait.
+template <typename TOut, int LN_VECTORS>
+__global__ __launch_bounds__(256) void layernorm_vector_kernel(
+    const float* __restrict__ x, const float* __restrict__ weight, const float* __restrict__ bias,
+    TOut* __restrict__ y, const int* __restrict__ rows, int hidden, float eps) {
+  __shared__ float scratch[32];
+  hx_pdl_trigger();
+  const int vectors = hidden >> 2;
+  float4 w[LN_VECTORS], b[LN_VECTORS];
+#pragma unroll
+  for (int i = 0; i < LN_VECTORS; ++i) {
+    const int v = threadIdx.x + i * 256;
+    b[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (v < vectors) {
+      w[i] = reinterpret_cast<const float4*>(weight)[v];
+      if (bias != nullptr) b[i] = reinterpret_cast<const float4*>(bias)[v];
+    }
+  }
+  hx_pdl_wait();
+  const int out_row = blockIdx.x;
+  const int in_row = rows != nullptr ? rows[out_row] : out_row;
+  const float4* xr = reinterpret_cast<const float4*>(x + static_cast<size_t>(in_row) * hidden);
+  float4 value[LN_VECTORS];
+  float sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < LN_VECTORS; ++i) {
+    const int v = threadIdx.x + i * 256;
+    if (v < vectors) {
+      value[i] = xr[v];
+      sum += (value[i].x + value[i].y) + (value[i].z + value[i].w);
+    }
+  }
+  const float mean = hx_block_sum(sum, scratch) / static_cast<float>(hidden);
+  float squares = 0.0f;
+#pragma unroll
+  for (int i = 0; i < LN_VECTORS; ++i) {
+    const int v = threadIdx.x + i * 256;
+    if (v < vectors) {
+      value[i].x -= mean; value[i].y -= mean; value[i].z -= mean; value[i].w -= mean;
+      squares = fmaf(value[i].x, value[i].x, squares);
+      squares = fmaf(value[i].y, value[i].y, squares);
+      squares = fmaf(value[i].z, value[i].z, squares);
+      squares = fmaf(value[i].w, value[i].w, squares);
+    }
+  }
+  const float variance = hx_block_sum(squares, scratch) / static_cast<float>(hidden);
+  const float inverse = 1.0f / sqrtf(variance + eps);
+  TOut* yr = y + static_cast<size_t>(out_row) * hidden;
+#pragma unroll
+  for (int i = 0; i < LN_VECTORS; ++i) {
+    const int v = threadIdx.x + i * 256;
+    if (v < vectors) {
+      const float p = value[i].x * inverse * w[i].x + b[i].x;
+      const float q = value[i].y * inverse * w[i].y + b[i].y;
+      const float r = value[i].z * inverse * w[i].z + b[i].z;
+      const float t = value[i].w * inverse * w[i].w + b[i].w;
+      if (sizeof(TOut) == 4) {
+        reinterpret_cast<float4*>(yr)[v] = make_float4(p, q, r, t);
+      } else {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(p, q);
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(r, t);
+        uint2 packed;
+        packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+        reinterpret_cast<uint2*>(yr)[v] = packed;
+      }
+    }
+  }
+}
+
 // bias may be null (a layer norm with a weight only).  `rows` as for hx_rmsnorm.
 HX_API int hx_layernorm(const float* x, const float* weight, const float* bias, void* y,
                         int out_dtype, const int* rows, int n_rows, int hidden, float eps,
@@ -347,6 +419,31 @@ HX_API int hx_layernorm(const float* x, const float* weight, const float* bias, 
   HX_REQUIRE(n_rows >= 0 && hidden > 0, "hx_layernorm: bad sizes");
   HX_REQUIRE(eps >= 0.0f, "hx_layernorm: eps must not be negative");
   if (n_rows == 0) return HX_OK;
+  HX_REQUIRE(out_dtype == HX_F32 || out_dtype == HX_BF16, "hx_layernorm: unknown dtype %d", out_dtype);
+  if (hidden % 4 == 0 && hidden <= 4 * 256 * 8 &&
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(weight) |
+        reinterpret_cast<uintptr_t>(bias) | reinterpret_cast<uintptr_t>(y)) & 15) == 0) {
+    const bool four = hidden <= 4 * 256 * 4;
+    if (out_dtype == HX_F32) {
+      float* out = static_cast<float*>(y);
+      if (four)
+        hx_launch(layernorm_vector_kernel<float, 4>, n_rows, 256, 0, stream, x, weight, bias, out,
+                  rows, hidden, eps);
+      else
+        hx_launch(layernorm_vector_kernel<float, 8>, n_rows, 256, 0, stream, x, weight, bias, out,
+                  rows, hidden, eps);
+    } else {
+      __nv_bfloat16* out = static_cast<__nv_bfloat16*>(y);
+      if (four)
+        hx_launch(layernorm_vector_kernel<__nv_bfloat16, 4>, n_rows, 256, 0, stream, x, weight,
+                  bias, out, rows, hidden, eps);
+      else
+        hx_launch(layernorm_vector_kernel<__nv_bfloat16, 8>, n_rows, 256, 0, stream, x, weight,
+                  bias, out, rows, hidden, eps);
+    }
+    HX_CHECK_LAUNCH("hx_layernorm");
+    return HX_OK;
+  }
   const int threads = hidden >= 1024 ? 256 : 128;
   if (out_dtype == HX_F32) {
     hx_launch(layernorm_kernel<float>, n_rows, threads, 0, stream, x, weight, bias,

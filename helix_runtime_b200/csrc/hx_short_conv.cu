@@ -137,6 +137,169 @@ __global__ __launch_bounds__(256) void short_conv_append_kernel(const ConvArgs<T
   }
 }
 
+// The same for bfloat16 rows made of whole 16-byte pieces (8 channels): one thread per piece,
+// every access 16 bytes wide (32 for the float32 accumulator), and a piece of a key or value
+// is exactly one 16-byte chunk of the cache layout.  Up to CONV_FAST_TAPS taps, whose weights
+// (and the token's place, its request and its page: the step's own description) are looked
+// up BEFORE the wait for the projection, while the projection still runs.
+constexpr int CONV_FAST_TAPS = 4;
+
+__device__ __forceinline__ void unpack8(const uint4& packed, float (&x)[8]) {
+  const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&packed);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 v = __bfloat1622float2(pairs[i]);
+    x[2 * i] = v.x;
+    x[2 * i + 1] = v.y;
+  }
+}
+
+__device__ __forceinline__ uint4 pack8(const float (&x)[8]) {
+  uint4 packed;
+  __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) pairs[i] = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+  return packed;
+}
+
+// eight projected values of `token` from column c, as the projection's store rounds them
+__device__ __forceinline__ uint4 projected8(const ConvArgs<__nv_bfloat16>& a, int token, int c) {
+  if (a.accum != nullptr) {
+    const float4* source =
+        reinterpret_cast<const float4*>(a.accum + static_cast<size_t>(token) * a.ld_accum + c);
+    const float4 lo = source[0], hi = source[1];
+    const float raw[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+    return pack8(raw);
+  }
+  return *reinterpret_cast<const uint4*>(a.raw + static_cast<size_t>(token) * a.ld_raw + c);
+}
+
+__device__ __forceinline__ void emit8(const ConvArgs<__nv_bfloat16>& a, int token, int position,
+                                      int table_row, int c, const uint4& packed) {
+  const int q_size = a.heads * a.head_dim;
+  if (c < q_size || !a.write_cache) {
+    *reinterpret_cast<uint4*>(a.out + static_cast<size_t>(token) * a.ld_out + c) = packed;
+    return;
+  }
+  const int kv_size = a.kv_heads * a.head_dim;
+  const bool is_key = c < q_size + kv_size;
+  const int within = c - q_size - (is_key ? 0 : kv_size);
+  const int kv_head = within / a.head_dim;
+  const int d = within - kv_head * a.head_dim;
+  const int page =
+      a.block_tables[static_cast<size_t>(table_row) * a.table_stride + position / a.page_size];
+  if (page < 0 || page >= a.num_pages) {
+    if (a.status != nullptr) atomicOr(a.status, HX_FLAG_BAD_PAGE);
+    return;
+  }
+  __nv_bfloat16* cache = is_key ? a.k_cache : a.v_cache;
+  *reinterpret_cast<uint4*>(cache + hx_cache_offset(page, kv_head, position % a.page_size, d,
+                                                    a.kv_heads, a.page_size, a.head_dim, 8)) = packed;
+}
+
+__global__ __launch_bounds__(256) void short_conv_append_pieces_kernel(
+    const ConvArgs<__nv_bfloat16> a) {
+  hx_pdl_trigger();
+  const int token = blockIdx.x;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  const int channels = (a.heads + 2 * a.kv_heads) * a.head_dim;
+  if (c >= a.total) {
+    hx_pdl_wait();      // a grid must not be seen complete before its predecessor is
+    return;
+  }
+  if (c >= channels) {      // passthrough: rounded and copied
+    hx_pdl_wait();
+    *reinterpret_cast<uint4*>(a.out + static_cast<size_t>(token) * a.ld_out + c) =
+        projected8(a, token, c);
+    return;
+  }
+  const int request = a.token_request[token];
+  const int start = a.request_start[request];
+  const int index = token - start;
+  const int reach = a.taps - 1;
+  if (index < reach && index != 0) {      // computed by the thread of the portion's first token
+    hx_pdl_wait();
+    return;
+  }
+  const int table_row = a.request_slot[request];
+  const int position = a.positions[token];
+  // w[j][i]: tap j of channel c + i
+  float w[CONV_FAST_TAPS][8];
+#pragma unroll
+  for (int j = 0; j < CONV_FAST_TAPS; ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      w[j][i] = j < a.taps ? a.filter[static_cast<size_t>(c + i) * a.taps + j] : 0.0f;
+  const int count = index == 0 ? a.request_start[request + 1] - start : 0;
+  hx_pdl_wait();
+
+  if (index >= reach) {
+    float y[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int j = 0; j < CONV_FAST_TAPS; ++j) {
+      if (j < a.taps) {
+        float u[8];
+        unpack8(projected8(a, token - reach + j, c), u);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) y[i] = fmaf(w[j][i], u[i], y[i]);
+      }
+    }
+    emit8(a, token, position, table_row, c, pack8(y));
+    return;
+  }
+  // the portion's first token: the tokens whose filter reaches behind the portion, then the
+  // new state (see the scalar kernel)
+  __nv_bfloat16* state = a.state + static_cast<size_t>(table_row) * reach * channels + c;
+  const int behind = count < reach ? count : reach;
+  for (int t = 0; t < behind; ++t) {
+    float y[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int j = 0; j < CONV_FAST_TAPS; ++j) {
+      if (j < a.taps) {
+        const int place = t - reach + j;
+        float u[8];
+        unpack8(place >= 0 ? projected8(a, start + place, c)
+                           : *reinterpret_cast<const uint4*>(
+                                 state + static_cast<size_t>(place + reach) * channels), u);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) y[i] = fmaf(w[j][i], u[i], y[i]);
+      }
+    }
+    emit8(a, start + t, position + t, table_row, c, pack8(y));
+  }
+  for (int r = 0; r < reach; ++r) {
+    const int place = count - reach + r;
+    const uint4 value = place >= 0 ? projected8(a, start + place, c)
+                                   : *reinterpret_cast<const uint4*>(
+                                         state + static_cast<size_t>(place + reach) * channels);
+    *reinterpret_cast<uint4*>(state + static_cast<size_t>(r) * channels) = value;
+  }
+}
+
+bool pieces_apply(const ConvArgs<__nv_bfloat16>& a) {
+  auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  return a.taps <= CONV_FAST_TAPS && a.head_dim % 8 == 0 && a.total % 8 == 0 &&
+         a.ld_out % 8 == 0 && aligned(a.out) && aligned(a.state) &&
+         (a.raw == nullptr || (a.ld_raw % 8 == 0 && aligned(a.raw))) &&
+         (a.accum == nullptr || (a.ld_accum % 4 == 0 && aligned(a.accum))) &&
+         (!a.write_cache || (aligned(a.k_cache) && aligned(a.v_cache)));
+}
+
+int launch_conv(const ConvArgs<__nv_bfloat16>& a, int tokens, cudaStream_t stream) {
+  if (!pieces_apply(a)) {
+    const dim3 grid(tokens, (a.total + 255) / 256);
+    HX_REQUIRE(grid.y <= 65535, "hx_short_conv_append: rows too wide");
+    hx_launch(short_conv_append_kernel<__nv_bfloat16>, grid, 256, 0, stream, a);
+    return HX_OK;
+  }
+  const int pieces = a.total / 8;
+  const int block = pieces >= 256 ? 256 : ((pieces + 31) / 32) * 32;
+  const dim3 grid(tokens, (pieces + block - 1) / block);
+  HX_REQUIRE(grid.y <= 65535, "hx_short_conv_append: rows too wide");
+  hx_launch(short_conv_append_pieces_kernel, grid, block, 0, stream, a);
+  return HX_OK;
+}
+
 template <typename T>
 int launch_conv(const ConvArgs<T>& a, int tokens, cudaStream_t stream) {
   const dim3 grid(tokens, (a.total + 255) / 256);
