@@ -91,6 +91,8 @@ struct TcPrefillArgs {
   float scale;
   int min_query_len;
   int* status;
+  int window;       // 0: every earlier key; else the query at p sees key j <= p with p - j < window
+  int keep_first;   // ... or j < keep_first (with a window only)
 };
 
 template <int D>
@@ -166,12 +168,23 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
   const int row0 = tile_in_request * LANES * BLOCK_M;         // first query row of the CTA
   const int rows_here = min(LANES * BLOCK_M, q_len - row0);
   const int last_key = context + row0 + rows_here - 1;        // last key any row here sees
-  const int n_tiles = last_key / BLOCK_N + 1;                 // key tiles somebody here sees
-  // lane l has rows [row0 + 128 l, ...) and sees the tiles before lane_tiles(l); lane 1 may be empty
+  // With a window the CTA walks the key tiles that hold kept first keys and then the tiles
+  // from the one with the first key its FIRST row sees through the window; `skipped` tiles lie
+  // between the two runs.  Every loop below counts TURNS: turn t works on key tile
+  // tile_at(t); rings and barriers go by turns, positions and pages by key tiles.  Keys from
+  // keep_first up to first_needed are seen by no row of the CTA: their pages may have been
+  // given back and are not read.
+  const int first_needed = a.window > 0 ? max(0, context + row0 - a.window + 1) : 0;
+  const int kept_tiles =
+      a.window > 0 ? min((a.keep_first + BLOCK_N - 1) / BLOCK_N, first_needed / BLOCK_N) : 0;
+  const int skipped = first_needed / BLOCK_N - kept_tiles;
+  auto tile_at = [&](int turn) { return turn < kept_tiles ? turn : turn + skipped; };
+  const int n_tiles = last_key / BLOCK_N + 1 - skipped;       // turns somebody here takes
+  // lane l has rows [row0 + 128 l, ...) and takes the turns before lane_tiles(l); lane 1 may be empty
   auto lane_rows = [&](int l) { return max(0, min(BLOCK_M, rows_here - l * BLOCK_M)); };
   auto lane_tiles = [&](int l) {
     const int rows = lane_rows(l);
-    return rows > 0 ? (context + row0 + l * BLOCK_M + rows - 1) / BLOCK_N + 1 : 0;
+    return rows > 0 ? (context + row0 + l * BLOCK_M + rows - 1) / BLOCK_N + 1 - skipped : 0;
   };
   const int page_size = a.page_size;
   const int pages_per_tile = BLOCK_N / page_size;
@@ -254,11 +267,15 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
       const int* table = a.block_tables +
                          static_cast<size_t>(a.request_table_row[request]) * a.table_stride;
       const int last_page = last_key / page_size;
-      auto pages_of = [&](int tile, int (&pages)[4]) {
+      auto pages_of = [&](int turn, int (&pages)[4]) {
 #pragma unroll
         for (int p = 0; p < 4; ++p) {
-          const int index = tile * pages_per_tile + p;
-          pages[p] = (p < pages_per_tile && index <= last_page) ? table[index] : -2;   // -2: none
+          const int index = tile_at(turn) * pages_per_tile + p;
+          // a page that holds no kept key and ends before the first key needed is not read
+          const bool wanted = index * page_size < a.keep_first ||
+                              (index + 1) * page_size > first_needed;
+          pages[p] = (p < pages_per_tile && index <= last_page && wanted) ? table[index]
+                                                                          : -2;   // -2: none
         }
       };
       int pages[4], next_pages[4];
@@ -499,11 +516,17 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
 #pragma unroll
           for (int i = 0; i < 16; ++i) p[c * 16 + i] = __uint_as_float(r[c][i]) * scale_log2;
       }
-      const int key0 = tile * BLOCK_N;
+      const int key0 = tile_at(tile) * BLOCK_N;
       if (key0 + BLOCK_N - 1 > q_position) {
 #pragma unroll
         for (int i = 0; i < BLOCK_N; ++i)
           if (key0 + i > q_position) p[i] = -INFINITY;
+      }
+      if (a.window > 0 && q_position - key0 >= a.window) {
+        // keys of the tile lie outside this row's window: they count only when kept
+#pragma unroll
+        for (int i = 0; i < BLOCK_N; ++i)
+          if (q_position - (key0 + i) >= a.window && key0 + i >= a.keep_first) p[i] = -INFINITY;
       }
       float part_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -511,7 +534,9 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
 #pragma unroll
         for (int u = 0; u < 4; ++u) part_max[u] = fmaxf(part_max[u], p[i + u]);
       const float tile_max = fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3]));
-      // key 0 is visible to every row, so the reference is finite from the first tile on
+      // without a window key 0 is visible to every row and the reference is finite from the
+      // first tile on; with one a row may see nothing of the CTA's first tiles and keeps
+      // -inf as its reference (and zeros as its probabilities) until it does
       if (tile == 0) {
         row_max = tile_max;
       } else if (__any_sync(0xffffffffu, tile_max > row_max + RAISE_MAXIMUM_BY)) {
@@ -520,7 +545,7 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
         // this warp's arrival below.  (o_full[b] completes a phase for every other tile; its
         // previous phase was complete before the scores of this tile were started.)
         const float new_max = fmaxf(row_max, tile_max);
-        const float correction = fast_exp2(row_max - new_max);
+        const float correction = row_max == -INFINITY ? 0.0f : fast_exp2(row_max - new_max);
         row_max = new_max;
         row_sum *= correction;
         ok = wait_for(&o_full[l * S_BUFFERS + (tile - 1) % S_BUFFERS],
@@ -544,11 +569,12 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
         }
       }
       float part_sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      const float reference = row_max == -INFINITY ? 0.0f : row_max;
 #pragma unroll
       for (int i = 0; i < BLOCK_N; i += 4)
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          p[i + u] = fast_exp2(p[i + u] - row_max);
+          p[i + u] = fast_exp2(p[i + u] - reference);
           part_sum[u] += p[i + u];
         }
       row_sum += (part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]);
@@ -577,15 +603,21 @@ __global__ __launch_bounds__(THREADS, 1) void prefill_attention_tc_kernel(TcPref
       // left there; a NaN would survive a zero probability, so they are cleared (by the group
       // that is first to need the tile: the other waits for its own arrival barrier only, but
       // the tile with the last key is seen by the last lane alone, or by lane 0 alone)
+      // The same goes for the keys between the kept ones and the first key needed, whose pages
+      // were not read.
       const int first_stale = last_key + 1 - key0;
-      if (first_stale < BLOCK_N) {
+      const int unseen_from = a.keep_first - key0;      // tile-relative; may be negative
+      const int unseen_to = first_needed - key0;        // exclusive
+      const bool has_unseen = a.window > 0 && unseen_to > 0 && unseen_from < BLOCK_N &&
+                              unseen_from < unseen_to;
+      if (first_stale < BLOCK_N || has_unseen) {
         ok = wait_for(&v_full[tile % V_STAGES], static_cast<uint32_t>(tile / V_STAGES) & 1u);
         if (!ok) break;
         uint8_t* v_half = v_stages + (tile % V_STAGES) * Config::kHalfBytes;
         for (int index = group_thread; index < BLOCK_N * (D / 8); index += 128) {
           const int key = index / (D / 8);
           const int piece = index - key * (D / 8);
-          if (key >= first_stale)
+          if (key >= first_stale || (has_unseen && key >= unseen_from && key < unseen_to))
             *reinterpret_cast<uint4*>(v_half + (key / page_size) * page_bytes +
                                       (piece * page_size + key % page_size) * 16) =
                 make_uint4(0u, 0u, 0u, 0u);
@@ -673,13 +705,17 @@ HX_API int hx_prefill_attention_tc_supports(int head_dim, int page_size) {
 
 // The arguments of hx_prefill_attention; tile_bound bounds the number of 256-token query tiles
 // (a larger bound only launches CTAs that leave at once).
-HX_API int hx_prefill_attention_tc(const void* q, int ldq, const void* k_cache,
-                                   const void* v_cache, const int* request_start,
-                                   const int* request_context, const int* request_table_row,
-                                   const int* block_tables, int table_stride, void* out, int ldo,
-                                   int requests, int tile_bound, int heads, int kv_heads,
-                                   int head_dim, int page_size, int num_pages, float scale,
-                                   int min_query_len, int* status, cudaStream_t stream) {
+HX_API int hx_prefill_attention_tc_windowed(const void* q, int ldq, const void* k_cache,
+                                            const void* v_cache, const int* request_start,
+                                            const int* request_context,
+                                            const int* request_table_row, const int* block_tables,
+                                            int table_stride, void* out, int ldo, int requests,
+                                            int tile_bound, int heads, int kv_heads, int head_dim,
+                                            int page_size, int num_pages, float scale,
+                                            int min_query_len, int window, int keep_first,
+                                            int* status, cudaStream_t stream) {
+  HX_REQUIRE(window >= 0 && keep_first >= 0, "hx_prefill_attention_tc: bad window");
+  if (window == 0) keep_first = 0;
   HX_REQUIRE(hx_prefill_attention_tc_supports(head_dim, page_size),
              "hx_prefill_attention_tc: head_dim %d with pages of %d is not supported (head sizes "
              "64 to 128 in steps of 16, pages of 16, 32 or 64)", head_dim, page_size);
@@ -698,7 +734,8 @@ HX_API int hx_prefill_attention_tc(const void* q, int ldq, const void* k_cache,
                   static_cast<const __nv_bfloat16*>(k_cache),
                   static_cast<const __nv_bfloat16*>(v_cache), request_start, request_context,
                   request_table_row, block_tables, table_stride, static_cast<__nv_bfloat16*>(out),
-                  ldo, requests, heads, kv_heads, page_size, num_pages, scale, min_query_len, status};
+                  ldo, requests, heads, kv_heads, page_size, num_pages, scale, min_query_len, status,
+                  window, keep_first};
   int rc;
   switch (head_dim) {
     case 64: rc = launch<64>(a, tile_bound, stream); break;
@@ -710,4 +747,19 @@ HX_API int hx_prefill_attention_tc(const void* q, int ldq, const void* k_cache,
   if (rc != HX_OK) return rc;
   HX_CHECK_LAUNCH("hx_prefill_attention_tc");
   return HX_OK;
+}
+
+// Every earlier key (no window).
+HX_API int hx_prefill_attention_tc(const void* q, int ldq, const void* k_cache,
+                                   const void* v_cache, const int* request_start,
+                                   const int* request_context, const int* request_table_row,
+                                   const int* block_tables, int table_stride, void* out, int ldo,
+                                   int requests, int tile_bound, int heads, int kv_heads,
+                                   int head_dim, int page_size, int num_pages, float scale,
+                                   int min_query_len, int* status, cudaStream_t stream) {
+  return hx_prefill_attention_tc_windowed(q, ldq, k_cache, v_cache, request_start,
+                                          request_context, request_table_row, block_tables,
+                                          table_stride, out, ldo, requests, tile_bound, heads,
+                                          kv_heads, head_dim, page_size, num_pages, scale,
+                                          min_query_len, 0, 0, status, stream);
 }

@@ -105,6 +105,9 @@ def _declare(library: ctypes.CDLL) -> None:
         _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int,
         _c_ptr, _c_ptr]
     library.hx_prefill_attention_windowed.restype = _c_int
+    library.hx_prefill_attention_tc_windowed.argtypes = \
+        library.hx_prefill_attention_windowed.argtypes
+    library.hx_prefill_attention_tc_windowed.restype = _c_int
     library.hx_prefill_attention_tc.argtypes = library.hx_prefill_attention.argtypes
     library.hx_prefill_attention_tc.restype = _c_int
     library.hx_prefill_attention_tc_supports.argtypes = [_c_int, _c_int]
@@ -511,15 +514,11 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     grid is exactly the tiles there are.
     ``tensor_memory``: take the tcgen05 kernel (scores, probabilities and output in tensor
     memory; pages of at least 16 keys) or the ``mma.sync`` kernel; default: tcgen05 where it
-    applies.  ``window`` > 0 (the query at position p sees key j <= p when p - j < window or
-    j < ``keep_first``) runs on the ``mma.sync`` kernel, which skips the tiles no row sees."""
+    applies.  ``window`` > 0: the query at position p sees key j <= p when p - j < window or
+    j < ``keep_first``; both kernels skip the tiles of keys that no row of a query tile sees."""
     _need(q, torch.bfloat16, "q")
     _need(k_cache, torch.bfloat16, "k_cache")
     _need(out, torch.bfloat16, "out")
-    if window:
-        if tensor_memory:
-            raise KernelError("the tcgen05 prompt attention has no window")
-        tensor_memory = False
     if tensor_memory is None:
         tensor_memory = prefill_attention_tc_supports(head_dim, page_size)
     if query_lengths is not None:
@@ -534,7 +533,8 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
         block_tables.stride(0), out.data_ptr(), out.stride(0), requests, tile_bound, heads,
         kv_heads, head_dim, page_size, num_pages, float(scale), min_query_len)
     if tensor_memory:
-        _check(lib().hx_prefill_attention_tc(*arguments, _ptr(status), _stream()))
+        _check(lib().hx_prefill_attention_tc_windowed(*arguments, int(window), int(keep_first),
+                                                      _ptr(status), _stream()))
     else:
         _check(lib().hx_prefill_attention_windowed(*arguments, int(window), int(keep_first),
                                                    _ptr(status), _stream()))

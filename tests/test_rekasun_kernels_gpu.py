@@ -215,6 +215,7 @@ def test_sigmoid_gate_and_the_accumulator_it_clears(dtype):
 
 def windowed_case(rng, dtype, heads, kv_heads, head_dim, page_size, context, new, window, keep,
                   dominant=None, tensor_cores=False, split_keys=32, free_dead_pages=True):
+    tensor_memory = tensor_cores == "tcgen05"
     """One request with ``context`` cached keys and ``new`` query tokens.  ``dominant=(row, key)``
     scales the key at that position along the query of that row.  Pages that no query of the
     step can see are taken out of the block table, as the cache manager does."""
@@ -254,7 +255,7 @@ def windowed_case(rng, dtype, heads, kv_heads, head_dim, page_size, context, new
         ops.prefill_attention(*common, starts, dev([context], torch.int32), slots,
                               dev(tables, torch.int32), out, 1, new // 64 + 1, heads, kv_heads,
                               head_dim, page_size, num_pages, scale, 1, status, window=window,
-                              keep_first=keep)
+                              keep_first=keep, tensor_memory=tensor_memory)
     else:
         longest = min(total, window + keep)
         max_splits = max(1, -(-longest // split_keys))
@@ -268,7 +269,10 @@ def windowed_case(rng, dtype, heads, kv_heads, head_dim, page_size, context, new
     return host(out), expected.transpose(1, 0, 2).reshape(new, -1).astype(np.float32), values
 
 
-KERNELS = [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)]
+# CUDA cores (float32), the streaming kernel (bfloat16 decode tokens and short portions), and
+# the two tensor-core kernels for prompt portions
+KERNELS = [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, "mma"),
+           (torch.bfloat16, "tcgen05")]
 
 
 @pytest.mark.parametrize("dtype,tensor_cores", KERNELS)
@@ -276,9 +280,11 @@ KERNELS = [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, Tru
                                          (65, 64), (200, 1)])
 def test_window_with_kept_keys_in_portions_and_decoding(dtype, tensor_cores, window, keep):
     rng = np.random.default_rng(30)
-    for context, new in [(0, 150), (37, 90), (210, 17)] + ([] if tensor_cores else [(129, 1), (15, 1)]):
-        out, expected, _ = windowed_case(rng, dtype, 4, 2, 32, 8, context, new, window, keep,
-                                         tensor_cores=tensor_cores)
+    for context, new in [(0, 150), (37, 90), (210, 17), (100, 300)] + \
+            ([] if tensor_cores else [(129, 1), (15, 1)]):
+        head_dim, page = (64, 16) if tensor_cores == "tcgen05" else (32, 8)
+        out, expected, _ = windowed_case(rng, dtype, 4, 2, head_dim, page, context, new, window,
+                                         keep, tensor_cores=tensor_cores)
         assert_close(out, expected, f"window {window} keep {keep} context {context} new {new}",
                      **tolerance(dtype, 2e-5))
 
@@ -291,7 +297,7 @@ def edge_keys(position, window, keep):
 
 
 @pytest.mark.parametrize("dtype,tensor_cores", KERNELS)
-@pytest.mark.parametrize("new", [1, 80])
+@pytest.mark.parametrize("new", [1, 80, 200])
 def test_one_key_at_every_edge_stands_out_or_is_not_seen(dtype, tensor_cores, new):
     """One key is scaled so that it would take all the weight of the last query: just inside
     the window or among the kept keys the output is that key's value, just outside it is what
@@ -301,8 +307,10 @@ def test_one_key_at_every_edge_stands_out_or_is_not_seen(dtype, tensor_cores, ne
     rng = np.random.default_rng(31)
     window, keep, context = 48, 6, 300 - new
     for key, seen in edge_keys(299, window, keep):
-        out, expected, values = windowed_case(rng, dtype, 4, 2, 32, 16, context, new, window, keep,
-                                              dominant=(new - 1, key), tensor_cores=tensor_cores)
+        head_dim = 64 if tensor_cores == "tcgen05" else 32
+        out, expected, values = windowed_case(rng, dtype, 4, 2, head_dim, 16, context, new, window,
+                                              keep, dominant=(new - 1, key),
+                                              tensor_cores=tensor_cores)
         assert_close(out, expected, f"key {key}", **tolerance(dtype, 2e-5))
         wanted = np.repeat(values[:, key], 2, axis=0).reshape(-1)
         distance = float(np.abs(out[-1] - wanted).max())

@@ -170,3 +170,39 @@ def test_greedy_generation_through_the_engine(name, dtype, models):
             assert logits[token] >= logits.max() - slack, \
                 f"token {token} at position {len(tokens)} is not the plain model's choice"
             tokens.append(token)
+
+
+@pytest.mark.parametrize("name,dtype", [("mixed", "float32"), ("fast", "bfloat16")])
+def test_trace_replay_as_a_user_runs_it(name, dtype, models, expectations, tmp_path):
+    """``bin/trace_run`` in a process of its own, fed a trace of mixed batches over a pool made
+    for the live requests only; the logits it writes are the plain implementation's."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    from conftest import ROOT
+    folder = models(name, dtype)[0]
+    requests = make_requests(name, extra=30)
+    expected = expectations(name, dtype, 30)
+    steps = traces.mixed(requests, max_live=4, seed=7)
+    out_dir = str(tmp_path / "out")
+    process = subprocess.Popen(
+        [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
+         "--out", out_dir, "--max-tokens", str(traces.live_token_need(steps, 64))],
+        stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, cwd=ROOT)
+    try:
+        positions = {}
+        for step in steps:
+            process.stdin.write(json.dumps(step) + "\n")
+            process.stdin.flush()
+            assert process.stdout.readline().strip() == f"done {step['step']}"
+            rows = traces.labels(step, positions)
+            data = np.fromfile(os.path.join(out_dir, f"{step['step']}.f32"), dtype="<f4")
+            want = np.stack([expected[request][position] for request, position in rows])
+            assert_close(data.reshape(want.shape), want, f"step {step['step']}", **TOLERANCE[dtype])
+        process.stdin.close()
+        assert process.wait(timeout=120) == 0
+    finally:
+        if process.poll() is None:
+            process.kill()
