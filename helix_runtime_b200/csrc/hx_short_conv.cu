@@ -197,10 +197,16 @@ __device__ __forceinline__ void emit8(const ConvArgs<__nv_bfloat16>& a, int toke
                                                     a.kv_heads, a.page_size, a.head_dim, 8)) = packed;
 }
 
+// A thread takes one piece (8 channels) of `run` consecutive tokens of the batch: the filter's
+// weights are fetched once (16 bytes a load), and a row of projected values is fetched once
+// and kept for the tokens behind it.
+template <int TAPS>
 __global__ __launch_bounds__(256) void short_conv_append_pieces_kernel(
-    const ConvArgs<__nv_bfloat16> a) {
+    const ConvArgs<__nv_bfloat16> a, int tokens, int run) {
   hx_pdl_trigger();
-  const int token = blockIdx.x;
+  constexpr int REACH = TAPS - 1;
+  const int first = blockIdx.x * run;
+  const int last = min(first + run, tokens);      // exclusive
   const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   const int channels = (a.heads + 2 * a.kv_heads) * a.head_dim;
   if (c >= a.total) {
@@ -209,70 +215,83 @@ __global__ __launch_bounds__(256) void short_conv_append_pieces_kernel(
   }
   if (c >= channels) {      // passthrough: rounded and copied
     hx_pdl_wait();
-    *reinterpret_cast<uint4*>(a.out + static_cast<size_t>(token) * a.ld_out + c) =
-        projected8(a, token, c);
+    for (int token = first; token < last; ++token)
+      *reinterpret_cast<uint4*>(a.out + static_cast<size_t>(token) * a.ld_out + c) =
+          projected8(a, token, c);
     return;
   }
-  const int request = a.token_request[token];
-  const int start = a.request_start[request];
-  const int index = token - start;
-  const int reach = a.taps - 1;
-  if (index < reach && index != 0) {      // computed by the thread of the portion's first token
-    hx_pdl_wait();
-    return;
+  // w[j][i]: tap j of channel c + i; the 8 * TAPS weights of the piece are contiguous
+  float w[TAPS][8];
+  {
+    float flat[8 * TAPS];
+    const float4* source = reinterpret_cast<const float4*>(a.filter + static_cast<size_t>(c) * TAPS);
+#pragma unroll
+    for (int v = 0; v < 2 * TAPS; ++v) {
+      const float4 x = source[v];
+      flat[4 * v] = x.x; flat[4 * v + 1] = x.y; flat[4 * v + 2] = x.z; flat[4 * v + 3] = x.w;
+    }
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) w[j][i] = flat[i * TAPS + j];
   }
-  const int table_row = a.request_slot[request];
-  const int position = a.positions[token];
-  // w[j][i]: tap j of channel c + i
-  float w[CONV_FAST_TAPS][8];
-#pragma unroll
-  for (int j = 0; j < CONV_FAST_TAPS; ++j)
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-      w[j][i] = j < a.taps ? a.filter[static_cast<size_t>(c + i) * a.taps + j] : 0.0f;
-  const int count = index == 0 ? a.request_start[request + 1] - start : 0;
   hx_pdl_wait();
 
-  if (index >= reach) {
-    float y[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+  // rows[j]: the projected values of batch row (token - REACH + j), whoever's they are; they
+  // are used only by a token that lies at least REACH tokens into its request's portion
+  uint4 rows[TAPS];
 #pragma unroll
-    for (int j = 0; j < CONV_FAST_TAPS; ++j) {
-      if (j < a.taps) {
+  for (int j = 0; j < REACH; ++j) {
+    const int row = first - REACH + j;
+    rows[j] = row >= 0 ? projected8(a, row, c) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  for (int token = first; token < last; ++token) {
+    rows[REACH] = projected8(a, token, c);
+    const int request = a.token_request[token];
+    const int start = a.request_start[request];
+    const int index = token - start;
+    const int table_row = a.request_slot[request];
+    if (index >= REACH) {
+      float y[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int j = 0; j < TAPS; ++j) {
         float u[8];
-        unpack8(projected8(a, token - reach + j, c), u);
+        unpack8(rows[j], u);
 #pragma unroll
         for (int i = 0; i < 8; ++i) y[i] = fmaf(w[j][i], u[i], y[i]);
       }
-    }
-    emit8(a, token, position, table_row, c, pack8(y));
-    return;
-  }
-  // the portion's first token: the tokens whose filter reaches behind the portion, then the
-  // new state (see the scalar kernel)
-  __nv_bfloat16* state = a.state + static_cast<size_t>(table_row) * reach * channels + c;
-  const int behind = count < reach ? count : reach;
-  for (int t = 0; t < behind; ++t) {
-    float y[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+      emit8(a, token, a.positions[token], table_row, c, pack8(y));
+    } else if (index == 0) {
+      // the portion's first token: the tokens whose filter reaches behind the portion, then
+      // the new state (see the scalar kernel)
+      const int count = a.request_start[request + 1] - start;
+      const int position = a.positions[token];
+      __nv_bfloat16* state = a.state + static_cast<size_t>(table_row) * REACH * channels + c;
+      const int behind = count < REACH ? count : REACH;
+      for (int t = 0; t < behind; ++t) {
+        float y[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-    for (int j = 0; j < CONV_FAST_TAPS; ++j) {
-      if (j < a.taps) {
-        const int place = t - reach + j;
-        float u[8];
-        unpack8(place >= 0 ? projected8(a, start + place, c)
-                           : *reinterpret_cast<const uint4*>(
-                                 state + static_cast<size_t>(place + reach) * channels), u);
+        for (int j = 0; j < TAPS; ++j) {
+          const int place = t - REACH + j;
+          float u[8];
+          unpack8(place >= 0 ? projected8(a, start + place, c)
+                             : *reinterpret_cast<const uint4*>(
+                                   state + static_cast<size_t>(place + REACH) * channels), u);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) y[i] = fmaf(w[j][i], u[i], y[i]);
+          for (int i = 0; i < 8; ++i) y[i] = fmaf(w[j][i], u[i], y[i]);
+        }
+        emit8(a, start + t, position + t, table_row, c, pack8(y));
+      }
+      for (int r = 0; r < REACH; ++r) {
+        const int place = count - REACH + r;
+        const uint4 value = place >= 0 ? projected8(a, start + place, c)
+                                       : *reinterpret_cast<const uint4*>(
+                                             state + static_cast<size_t>(place + REACH) * channels);
+        *reinterpret_cast<uint4*>(state + static_cast<size_t>(r) * channels) = value;
       }
     }
-    emit8(a, start + t, position + t, table_row, c, pack8(y));
-  }
-  for (int r = 0; r < reach; ++r) {
-    const int place = count - reach + r;
-    const uint4 value = place >= 0 ? projected8(a, start + place, c)
-                                   : *reinterpret_cast<const uint4*>(
-                                         state + static_cast<size_t>(place + reach) * channels);
-    *reinterpret_cast<uint4*>(state + static_cast<size_t>(r) * channels) = value;
+#pragma unroll
+    for (int j = 0; j < REACH; ++j) rows[j] = rows[j + 1];
   }
 }
 
@@ -292,11 +311,17 @@ int launch_conv(const ConvArgs<__nv_bfloat16>& a, int tokens, cudaStream_t strea
     hx_launch(short_conv_append_kernel<__nv_bfloat16>, grid, 256, 0, stream, a);
     return HX_OK;
   }
+  const int run = tokens >= 1024 ? 8 : (tokens >= 256 ? 2 : 1);
   const int pieces = a.total / 8;
   const int block = pieces >= 256 ? 256 : ((pieces + 31) / 32) * 32;
-  const dim3 grid(tokens, (pieces + block - 1) / block);
+  const dim3 grid((tokens + run - 1) / run, (pieces + block - 1) / block);
   HX_REQUIRE(grid.y <= 65535, "hx_short_conv_append: rows too wide");
-  hx_launch(short_conv_append_pieces_kernel, grid, block, 0, stream, a);
+  switch (a.taps) {
+    case 1: hx_launch(short_conv_append_pieces_kernel<1>, grid, block, 0, stream, a, tokens, run); break;
+    case 2: hx_launch(short_conv_append_pieces_kernel<2>, grid, block, 0, stream, a, tokens, run); break;
+    case 3: hx_launch(short_conv_append_pieces_kernel<3>, grid, block, 0, stream, a, tokens, run); break;
+    default: hx_launch(short_conv_append_pieces_kernel<4>, grid, block, 0, stream, a, tokens, run); break;
+  }
   return HX_OK;
 }
 

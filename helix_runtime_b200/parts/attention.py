@@ -222,8 +222,10 @@ class PagedAttention(Mixer):
     def project_filtered(self, ctx: StepContext, cache: LayerCache, x: torch.Tensor,
                          qkv: torch.Tensor) -> Optional[torch.Tensor]:
         """Projection, causal filter over time and cache append.  Leaves the filtered queries
-        (and the gate's projection, when it is fused) in ``qkv``; returns the float32
-        accumulator the projection summed into, which is still to be cleared, or None."""
+        in ``qkv``.  Returns the float32 accumulator the projection summed into, which is still
+        to be cleared (or None), and the buffer whose columns behind q, k and v hold the gate's
+        projection when it is fused: the projected rows themselves, or ``qkv`` when the
+        projection arrived as sums (the filter kernel then rounds and copies those columns)."""
         n = ctx.n_tokens
         write = cache.owns and cache.keys is not None
         appends = self.conv_appends and write
@@ -240,11 +242,12 @@ class PagedAttention(Mixer):
                               ctx.token_request, ctx.request_slot, ctx.request_start,
                               cache.block_tables if appends else None,
                               cache.keys if appends else None, cache.values if appends else None,
-                              n, self.heads, self.kv_heads, self.row_dim, self.projected_size,
+                              n, self.heads, self.kv_heads, self.row_dim,
+                              self.projected_size if raw is None else self.qkv_size,
                               cache.page_size, cache.num_pages, ctx.status)
         if not self.conv_appends:
             self.position.apply(ctx, cache, qkv, self.heads, self.kv_heads)
-        return accumulator
+        return accumulator, (qkv if raw is None else raw)
 
     def split_keys_for(self, tokens: int, longest: int, limit: int) -> int:
         """Keys per split.  One warp walks one (token, head, split); a step with few tokens
@@ -262,9 +265,9 @@ class PagedAttention(Mixer):
         n = ctx.n_tokens
         qkv = ctx.workspace.get("attention.qkv", (ctx.capacity, self.projected_size), ctx.dtype)
         context = ctx.workspace.get("attention.context", (ctx.capacity, self.q_size), ctx.dtype)
-        uncleared = None
+        uncleared = gate_rows = None
         if self.conv_taps > 1:
-            uncleared = self.project_filtered(ctx, cache, x, qkv)
+            uncleared, gate_rows = self.project_filtered(ctx, cache, x, qkv)
         elif is_weight_stream(x, self.w_qkv, n):
             # few tokens: split-K into a float32 accumulator that the rotary kernel reads,
             # rounds as the product's store would have, and clears
@@ -314,7 +317,7 @@ class PagedAttention(Mixer):
                                 arrivals=arrivals, keep_first=kept)
         if self.gated:
             if self.fused_gate:
-                gate = qkv[:, self.qkv_size:]
+                gate = gate_rows[:, self.qkv_size:]
             else:
                 gate = ctx.workspace.get("attention.gate", (ctx.capacity, self.q_size), ctx.dtype)
                 project(x, self.w_g, gate, n, ops.EPI_STORE, ctx.status)
