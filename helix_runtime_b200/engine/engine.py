@@ -185,7 +185,14 @@ class Engine:
         self.config = config
         device = require_cuda(model.device)
         kv_needs, state_needs = model.cache_needs()
-        pages_per_request = -(-model.max_positions // config.page_size)
+        # the most positions a request holds pages for at once: all of them in a layer that
+        # keeps every key; in a windowed layer the window, its kept first keys, the portion
+        # a step feeds and the page being filled
+        held = max((model.max_positions if need.window is None else
+                    min(model.max_positions, need.window + need.keep_first
+                        + config.max_tokens_per_iteration + 2 * config.page_size)
+                    for need in kv_needs.values()), default=model.max_positions)
+        pages_per_request = -(-held // config.page_size)
         num_pages = config.num_pages or pages_per_request * config.max_running_requests
         if config.num_pages is None and config.cache_memory_fraction is not None:
             if not 0.0 < config.cache_memory_fraction <= 1.0:

@@ -231,12 +231,12 @@ class PagedAttention(Mixer):
         appends = self.conv_appends and write
         accumulator = raw = None
         if is_weight_stream(x, self.w_qkv, n):
-            accumulator = ctx.workspace.accumulator("attention.projected",
+            accumulator = ctx.workspace.accumulator(f"attention.projected/{self.projected_size}",
                                                     (STREAMING_MAX_TOKENS, self.projected_size))
             project_into_accumulator(x, self.w_qkv, accumulator, n, ctx.status, ctx.ordered_sums)
         else:
-            raw = ctx.workspace.get("attention.projected", (ctx.capacity, self.projected_size),
-                                    ctx.dtype)
+            raw = ctx.workspace.get(f"attention.projected/{self.projected_size}",
+                                    (ctx.capacity, self.projected_size), ctx.dtype)
             project(x, self.w_qkv, raw, n, ops.EPI_STORE, ctx.status)
         ops.short_conv_append(raw, accumulator, qkv, self.conv_filter, cache.state, ctx.positions,
                               ctx.token_request, ctx.request_slot, ctx.request_start,
@@ -263,15 +263,19 @@ class PagedAttention(Mixer):
     def forward(self, ctx: StepContext, cache: LayerCache, x: torch.Tensor,
                 residual: torch.Tensor) -> None:
         n = ctx.n_tokens
-        qkv = ctx.workspace.get("attention.qkv", (ctx.capacity, self.projected_size), ctx.dtype)
-        context = ctx.workspace.get("attention.context", (ctx.capacity, self.q_size), ctx.dtype)
+        # scratch is named by its width: layers of different sizes each keep their own buffer
+        # (a name whose shape changed from layer to layer would be replaced at every call)
+        qkv = ctx.workspace.get(f"attention.qkv/{self.projected_size}",
+                                (ctx.capacity, self.projected_size), ctx.dtype)
+        context = ctx.workspace.get(f"attention.context/{self.q_size}",
+                                    (ctx.capacity, self.q_size), ctx.dtype)
         uncleared = gate_rows = None
         if self.conv_taps > 1:
             uncleared, gate_rows = self.project_filtered(ctx, cache, x, qkv)
         elif is_weight_stream(x, self.w_qkv, n):
             # few tokens: split-K into a float32 accumulator that the rotary kernel reads,
             # rounds as the product's store would have, and clears
-            accumulator = ctx.workspace.accumulator("attention.qkv",
+            accumulator = ctx.workspace.accumulator(f"attention.qkv/{self.qkv_size}",
                                                     (STREAMING_MAX_TOKENS, self.qkv_size))
             project_into_accumulator(x, self.w_qkv, accumulator, n, ctx.status,
                                      ctx.ordered_sums)
@@ -306,7 +310,7 @@ class PagedAttention(Mixer):
             floats = ops.attention_scratch_floats(n, self.heads, self.row_dim, max_splits,
                                                   ctx.dtype, cache.page_size, window)
             partial = ctx.workspace.at_least("attention.partial", floats, torch.float32)
-            arrivals = ctx.workspace.accumulator("attention.arrivals",
+            arrivals = ctx.workspace.accumulator(f"attention.arrivals/{self.heads}",
                                                  (ctx.capacity * self.heads,), torch.int32)
             ops.paged_attention(qkv, cache.keys, cache.values, ctx.positions, ctx.token_request,
                                 ctx.request_slot, cache.block_tables, context, partial, n,
@@ -319,7 +323,8 @@ class PagedAttention(Mixer):
             if self.fused_gate:
                 gate = gate_rows[:, self.qkv_size:]
             else:
-                gate = ctx.workspace.get("attention.gate", (ctx.capacity, self.q_size), ctx.dtype)
+                gate = ctx.workspace.get(f"attention.gate/{self.q_size}",
+                                         (ctx.capacity, self.q_size), ctx.dtype)
                 project(x, self.w_g, gate, n, ops.EPI_STORE, ctx.status)
             ops.sigmoid_gate(context, gate, n, self.q_size, clear=uncleared)
         elif uncleared is not None:

@@ -49,7 +49,8 @@ class GatedMlp(FeedForward):
 
     def forward(self, ctx: StepContext, x: torch.Tensor, residual: torch.Tensor) -> None:
         n = ctx.n_tokens
-        act = ctx.workspace.get("mlp.act", (ctx.capacity, self.intermediate), ctx.dtype)
+        act = ctx.workspace.get(f"mlp.act/{self.intermediate}", (ctx.capacity, self.intermediate),
+                                ctx.dtype)
         project_swiglu(x, self.w_gate_up, self.intermediate, act, ctx.workspace, ctx.capacity, n,
                        ctx.status, ctx.ordered_sums, self.activation)
         project(act, self.w_down, residual, n, ops.EPI_ADD_F32, ctx.status, ctx.ordered_sums)

@@ -142,7 +142,8 @@ def project_swiglu(x: torch.Tensor, w_gate_up: Weight, intermediate: int, act: t
     if tokens == 0:
         return
     if is_weight_stream(x, w_gate_up, tokens):
-        accumulator = workspace.accumulator("mlp.gate_up", (STREAMING_MAX_TOKENS, 2 * intermediate))
+        accumulator = workspace.accumulator(f"mlp.gate_up/{intermediate}",
+                                            (STREAMING_MAX_TOKENS, 2 * intermediate))
         project_into_accumulator(x, w_gate_up, accumulator, tokens, status, ordered)
         ops.swiglu(accumulator[:tokens], act[:tokens], zero_input=True, activation=activation)
     elif uses_tensor_cores(x, w_gate_up, tokens):
@@ -150,6 +151,7 @@ def project_swiglu(x: torch.Tensor, w_gate_up: Weight, intermediate: int, act: t
         _gemm_tc(x, w_gate_up, act, tokens, intermediate, epilogue, status,
                  up_row_offset=intermediate)
     else:
-        scratch = workspace.get("mlp.gate_up", (capacity, 2 * intermediate), torch.float32)
+        scratch = workspace.get(f"mlp.gate_up/{intermediate}", (capacity, 2 * intermediate),
+                                torch.float32)
         _gemm_simt(x, w_gate_up, scratch, tokens, ops.EPI_STORE_F32)
         ops.swiglu(scratch[:tokens], act[:tokens], activation=activation)

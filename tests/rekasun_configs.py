@@ -1,6 +1,6 @@
 """Small Rekasun configurations for the tests and how their model folders are made.
 
-The three differ in every size and constant, and inside a model the layers differ too:
+They differ in every size and constant, and inside a model the layers differ too:
 
 * ``mixed``: three layers of different shapes (so three cache groups): grouped heads with a
   3-tap filter, a window of 24 and 4 kept keys; equal query and key/value heads whose values
@@ -13,6 +13,9 @@ The three differ in every size and constant, and inside a model the layers diffe
 * ``fast``: the shapes the tensor-core kernels are built for (width 256, heads of 64, a
   feed-forward of 512, pages of 16), a window of 48 with 8 kept keys, the middle layer run
   twice, prompts of hundreds of tokens.
+
+* ``odd``: sizes the fast kernels do not take: a width (90) that is no multiple of 8, heads
+  of 20 with values of 12, five filter taps, an odd vocabulary, a loop that runs once.
 
 Weights are drawn so that attention is sharp (scores spread by about two), filters and
 biases are not trivial, and norm weights are not one.
@@ -61,9 +64,16 @@ CONFIGS = {
                    _layer(_attention(4, 4, 64, 64, 2, 100, 0), 512)],
         "loop": {"start": 1, "stop": 2, "times": 2},
     },
+    "odd": {
+        "architecture": "Rekasun", "vocab": 131, "width": 90,
+        "embedding": {"scale": 0.7}, "norm": {"eps": 1e-4},
+        "layers": [_layer(_attention(3, 3, 20, 12, 5, 33, 1), 70),
+                   _layer(_attention(6, 2, 20, 12, 5, 33, 1), 50)],
+        "loop": {"start": 1, "stop": 2, "times": 1},
+    },
 }
-PAGE_SIZE = {"mixed": 8, "plain": 16, "fast": 16}
-SEED = {"mixed": 11, "plain": 12, "fast": 13}
+PAGE_SIZE = {"mixed": 8, "plain": 16, "fast": 16, "odd": 8}
+SEED = {"mixed": 11, "plain": 12, "fast": 13, "odd": 14}
 
 
 def tensors_for(config: dict, seed: int, storage_dtype: torch.dtype):

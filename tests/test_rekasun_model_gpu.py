@@ -16,9 +16,10 @@ from rekasun_configs import CONFIGS, PAGE_SIZE, make_folder
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"mixed": (1, 2, 9, 33, 90), "plain": (3, 17, 40, 75), "fast": (5, 70, 150, 310)}
-CASES = [("mixed", "float32"), ("plain", "float32"), ("fast", "float32"),
-         ("mixed", "bfloat16"), ("plain", "bfloat16"), ("fast", "bfloat16")]
+LENGTHS = {"mixed": (1, 2, 9, 33, 90), "plain": (3, 17, 40, 75), "fast": (5, 70, 150, 310),
+           "odd": (4, 11, 50, 120)}
+CASES = [("mixed", "float32"), ("plain", "float32"), ("fast", "float32"), ("odd", "float32"),
+         ("mixed", "bfloat16"), ("plain", "bfloat16"), ("fast", "bfloat16"), ("odd", "bfloat16")]
 # float32: double against float32 sums.  bfloat16: the plain implementation rounds where the
 # engine stores; what is left are activations that fall on the other side of a rounding
 # boundary, which sharp attention carries into logits of spread one.
@@ -76,6 +77,24 @@ def test_whole_requests(name, dtype, models, expectations):
     harness = Harness(models(name, dtype)[0], dtype, PAGE_SIZE[name], num_pages=48)
     replay(harness, traces.whole(make_requests(name)), expectations(name, dtype), dtype,
            f"whole {name} {dtype}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layers_of_different_sizes_keep_their_scratch(dtype, models):
+    """Every layer's scratch buffers stay where they are from step to step (CUDA graphs point
+    at them), also when the layers of a model differ in width."""
+    harness = Harness(models("mixed", dtype)[0], dtype, PAGE_SIZE["mixed"], num_pages=48)
+    tokens = make_requests("mixed")["r3"]
+    harness.run([("a", tokens[:19], [18])])
+    harness.run([("a", tokens[19:20], [0])])      # a portion and a single token: every path's buffers
+    workspace = harness.step.workspace
+    held, retired = workspace.bytes(), len(workspace._retired)
+    for position in range(20, 30):
+        harness.run([("a", tokens[position:position + 1], [0])])
+    harness.run([("b", tokens[:17], [16])])
+    harness.end("b")
+    assert workspace.bytes() == held and len(workspace._retired) == retired
+    harness.end("a")
 
 
 @pytest.mark.parametrize("name,dtype", CASES)
@@ -206,3 +225,28 @@ def test_trace_replay_as_a_user_runs_it(name, dtype, models, expectations, tmp_p
     finally:
         if process.poll() is None:
             process.kill()
+
+
+def test_generation_from_the_command_line(models):
+    """``bin/helix_generate`` chooses the model by ``config.json`` and prints the plain
+    implementation's greedy tokens."""
+    import os
+    import subprocess
+    import sys
+
+    from conftest import ROOT
+    folder, plain = models("mixed", "float32")
+    prompt = random_tokens(CONFIGS["mixed"]["vocab"], 19, seed=3)
+    done = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "bin", "helix_generate"), "--model", folder,
+         "--dtype", "float32", "--max-new-tokens", "12", *[str(token) for token in prompt]],
+        capture_output=True, text=True, cwd=ROOT, timeout=300)
+    assert done.returncode == 0, done.stderr
+    lines = done.stdout.strip().splitlines()
+    generated = [int(token) for token in lines[0].split(":")[1].split()]
+    tokens = list(prompt)
+    for token in generated:
+        logits = plain.logits(tokens)[-1]
+        assert logits[token] >= logits.max() - 1e-3
+        tokens.append(token)
+    assert len(generated) == 12 and lines[1] == "stop_reason: max_new_tokens"
