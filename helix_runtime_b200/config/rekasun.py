@@ -13,10 +13,17 @@ import dataclasses
 from typing import Any, Dict, Mapping, Optional, Tuple
 
 from .errors import ConfigError
-from .keys import COUNT, REAL, TEXT, Key, read_keys
+import math
+
+from .keys import COUNT, REAL, TEXT, Key, Kind, read_keys
 
 ARCHITECTURE = "Rekasun"
 DEFAULT_MAX_POSITIONS = 1 << 17
+
+
+# a constant that multiplies: any finite number
+FACTOR = Kind(lambda value: isinstance(value, (int, float)) and not isinstance(value, bool)
+              and math.isfinite(float(value)), float, "must be a finite number")
 
 
 def _whole(value: Any) -> bool:
@@ -142,7 +149,7 @@ class RekasunConfig:
     def from_dict(cls, document: Mapping[str, Any]) -> "RekasunConfig":
         values = read_keys(document, (Key("vocab", COUNT), Key("width", COUNT),
                                       Key("max_positions", COUNT, default=DEFAULT_MAX_POSITIONS)))
-        scale = read_keys(document.get("embedding") or {}, (Key("scale", REAL, default=1.0),),
+        scale = read_keys(document.get("embedding") or {}, (Key("scale", FACTOR, default=1.0),),
                           "embedding.")["scale"]
         eps = read_keys(_object(document, "norm"), (Key("eps", REAL),), "norm.")["eps"]
         layers = document.get("layers")
