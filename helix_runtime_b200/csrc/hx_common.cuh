@@ -226,7 +226,8 @@ __device__ __forceinline__ float hx_silu_fast(float x) {
 }
 
 // What a gated feed-forward passes its gate through before the product with the up
-// projection.  gelu_tanh(z) = 0.5 z (1 + tanh(u)), u = sqrt(2/pi) (z + 0.044715 z^3); since
+// projection.  gelu_tanh is GELU's tanh approximation, z/2 * (1 + tanh(u)) with
+// u = c (z + a z^3), c = sqrt(2/pi), a = 0.044715; since
 // 0.5 (1 + tanh(u)) = sigmoid(2u), it is z * sigmoid(2u) and shares the stable sigmoid.
 enum HxGateActivation : int { HX_GATE_SILU = 0, HX_GATE_GELU_TANH = 1 };
 

@@ -1,7 +1,8 @@
 """Gated feed-forward: ``down(act(gate(x)) * up(x))`` (src/model/cpu_llama.cpp:93-98).
 
 Parameters: ``intermediate_size``, ``activation`` (``silu``, or ``gelu_tanh``:
-``0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))``).  Tensors: ``gate``, ``up``
+the tanh approximation of GELU, ``z * sigmoid(2 c (z + a z^3))`` with ``c = sqrt(2/pi)``,
+``a = 0.044715``).  Tensors: ``gate``, ``up``
 ``[intermediate, hidden]`` and ``down`` ``[hidden, intermediate]``.  gate and up are
 fused into one ``[2I, H]`` matrix at load so that both products read the input once;
 on the tensor cores the gated activation is the epilogue of that product.

@@ -83,7 +83,8 @@ int hx_swiglu(float* gate_up, void* act, int out_dtype, int tokens, int intermed
               int zero_input, cudaStream_t stream);
 
 /* act[t, f] = g(gate_up[t, f]) * gate_up[t, intermediate + f]; activation 0: g = silu,
-   1: g = gelu_tanh, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))) */
+   1: g = the tanh approximation of GELU, z * sigmoid(2 c (z + a z^3)) with c = sqrt(2/pi),
+   a = 0.044715 */
 int hx_gated_activation(float* gate_up, void* act, int out_dtype, int tokens, int intermediate,
                         int ld_in, int zero_input, int activation, cudaStream_t stream);
 /* context[t, :width] *= sigmoid(gate[t, :width]); clear (may be null): float32 rows

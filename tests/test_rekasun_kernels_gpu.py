@@ -305,7 +305,7 @@ def test_one_key_at_every_edge_stands_out_or_is_not_seen(dtype, tensor_cores, ne
     if tensor_cores and new == 1:
         pytest.skip("single tokens are the CUDA-core kernel's")
     rng = np.random.default_rng(31)
-    window, keep, context = 48, 6, 300 - new
+    window, keep, context = 48, 5, 300 - new
     for key, seen in edge_keys(299, window, keep):
         head_dim = 64 if tensor_cores == "tcgen05" else 32
         out, expected, values = windowed_case(rng, dtype, 4, 2, head_dim, 16, context, new, window,
