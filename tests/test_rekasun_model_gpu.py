@@ -250,3 +250,38 @@ def test_generation_from_the_command_line(models):
         assert logits[token] >= logits.max() - 1e-3
         tokens.append(token)
     assert len(generated) == 12 and lines[1] == "stop_reason: max_new_tokens"
+
+
+@pytest.mark.parametrize("cuda_graphs", [False, True])
+def test_the_next_turn_of_a_conversation_adopts_pages_kept_keys_and_filter_state(models, cuda_graphs):
+    """Prefix sharing: a later prompt that goes on from an earlier one adopts the pages its
+    windows still reach, the kept first pages, and the filters' state as it stood at the
+    prefix's end, and computes only what is new; its tokens are the plain implementation's."""
+    from helix_runtime_b200 import Engine
+    folder, plain = models("mixed", "float32")
+    vocab = CONFIGS["mixed"]["vocab"]
+    engine = Engine.from_pretrained(folder, dtype="float32", page_size=8, num_pages=96,
+                                    max_running_requests=3, max_tokens_per_iteration=32,
+                                    max_prefill_chunk=11, cuda_graphs=cuda_graphs,
+                                    prefix_cache_entries=4, poison_free_pages=True)
+
+    def check(prompt, result):
+        logits = plain.logits(prompt + result.generated_tokens[:-1])
+        for index, token in enumerate(result.generated_tokens):
+            row = logits[len(prompt) + index - 1]
+            assert row[token] >= row.max() - 1e-3, f"token {index}"
+
+    first = random_tokens(vocab, 45, seed=41)                 # its prefix: 40 tokens
+    one = engine.generate([first], max_new_tokens=6)[0]
+    check(first, one)
+    second = first + one.generated_tokens + random_tokens(vocab, 30, seed=42)
+    other = random_tokens(vocab, 13, seed=43)
+    two, beside = engine.generate([second, other], max_new_tokens=8)
+    check(second, two)
+    check(other, beside)
+    assert engine.request(two.request_id).reused_tokens == 40
+    assert engine.request(beside.request_id).reused_tokens == 0
+    engine.cache.check()
+    engine.prefix.clear()
+    engine.cache.check()
+    assert all(group.pool.pages_in_use == 0 for group in engine.cache.groups)
