@@ -235,22 +235,30 @@ __global__ __launch_bounds__(256) void short_conv_append_pieces_kernel(
 #pragma unroll
       for (int i = 0; i < 8; ++i) w[j][i] = flat[i * TAPS + j];
   }
+  // the run's first token (in decoding the only one): its request, place and position are
+  // the step's own description and are looked up while the projection still runs
+  const int first_request = a.token_request[first];
+  const int first_start = a.request_start[first_request];
+  const int first_slot = a.request_slot[first_request];
+  const int first_position = a.positions[first];
   hx_pdl_wait();
 
-  // rows[j]: the projected values of batch row (token - REACH + j), whoever's they are; they
-  // are used only by a token that lies at least REACH tokens into its request's portion
+  // rows[j]: the projected values of batch row (token - REACH + j); they are used only by a
+  // token that lies at least REACH tokens into its request's portion
   uint4 rows[TAPS];
 #pragma unroll
   for (int j = 0; j < REACH; ++j) {
     const int row = first - REACH + j;
-    rows[j] = row >= 0 ? projected8(a, row, c) : make_uint4(0u, 0u, 0u, 0u);
+    // (rows of another request are never used: not fetched)
+    rows[j] = row >= first_start ? projected8(a, row, c) : make_uint4(0u, 0u, 0u, 0u);
   }
   for (int token = first; token < last; ++token) {
     rows[REACH] = projected8(a, token, c);
-    const int request = a.token_request[token];
-    const int start = a.request_start[request];
+    const bool head = token == first;
+    const int request = head ? first_request : a.token_request[token];
+    const int start = head ? first_start : a.request_start[request];
     const int index = token - start;
-    const int table_row = a.request_slot[request];
+    const int table_row = head ? first_slot : a.request_slot[request];
     if (index >= REACH) {
       float y[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
@@ -260,12 +268,12 @@ __global__ __launch_bounds__(256) void short_conv_append_pieces_kernel(
 #pragma unroll
         for (int i = 0; i < 8; ++i) y[i] = fmaf(w[j][i], u[i], y[i]);
       }
-      emit8(a, token, a.positions[token], table_row, c, pack8(y));
+      emit8(a, token, head ? first_position : a.positions[token], table_row, c, pack8(y));
     } else if (index == 0) {
       // the portion's first token: the tokens whose filter reaches behind the portion, then
       // the new state (see the scalar kernel)
       const int count = a.request_start[request + 1] - start;
-      const int position = a.positions[token];
+      const int position = head ? first_position : a.positions[token];
       __nv_bfloat16* state = a.state + static_cast<size_t>(table_row) * REACH * channels + c;
       const int behind = count < REACH ? count : REACH;
       for (int t = 0; t < behind; ++t) {
