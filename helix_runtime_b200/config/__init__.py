@@ -1,12 +1,14 @@
 from .errors import ConfigError
 from .llama import LlamaConfig
 from .rekasun import RekasunConfig
+from .zuzadra import ZuzadraConfig
 from .registry import (Architecture, architecture_for, known_architectures, load_config,
                        read_config_json, register_architecture)
 from .spec import BlockSpec, ModelSpec, PartSpec, ScheduleEntry
 
 __all__ = [
     "Architecture", "BlockSpec", "ConfigError", "LlamaConfig", "ModelSpec", "PartSpec", "RekasunConfig",
+    "ZuzadraConfig",
     "ScheduleEntry", "architecture_for", "known_architectures", "load_config",
     "read_config_json", "register_architecture",
 ]

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import dataclasses
 import os
-from typing import Any, Callable, Dict, Mapping, Tuple
+from typing import Any, Callable, Dict, Mapping, Optional, Tuple
 
 from .errors import ConfigError
 from .strict_json import parse_object
@@ -23,6 +23,9 @@ class Architecture:
     config_from_dict: Callable[[Mapping[str, Any]], Any]
     build_spec: Callable[[Any], ModelSpec]
     aliases: Tuple[str, ...] = ()
+    # sizes that the configuration leaves to the checkpoint: ``(config, shapes) -> config`` with
+    # ``shapes`` the checkpoint's tensor shapes by name; None: the configuration has them all
+    sizes_from_checkpoint: Optional[Callable[[Any, Mapping[str, Tuple[int, ...]]], Any]] = None
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
@@ -30,14 +33,17 @@ _ARCHITECTURES: Dict[str, Architecture] = {}
 
 def register_architecture(name: str, config_from_dict: Callable[[Mapping[str, Any]], Any],
                           build_spec: Callable[[Any], ModelSpec],
-                          aliases: Tuple[str, ...] = ()) -> Architecture:
+                          aliases: Tuple[str, ...] = (),
+                          sizes_from_checkpoint=None) -> Architecture:
     """Register ``name`` (the string in ``config.json``'s ``architectures``).
 
     ``config_from_dict`` turns the parsed JSON object into a typed configuration
     (raising :class:`ConfigError`), ``build_spec`` turns that configuration into
     the part-by-part :class:`ModelSpec`.  ``aliases`` are ``model_type`` values.
+    ``sizes_from_checkpoint(config, shapes)`` completes a configuration with sizes that only the
+    checkpoint's tensor shapes give.
     """
-    entry = Architecture(name, config_from_dict, build_spec, tuple(aliases))
+    entry = Architecture(name, config_from_dict, build_spec, tuple(aliases), sizes_from_checkpoint)
     for key in (name, *aliases):
         existing = _ARCHITECTURES.get(key)
         if existing is not None and existing.name != name:

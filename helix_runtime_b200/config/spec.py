@@ -42,6 +42,9 @@ class BlockSpec:
     ``x += mixer(norm(x)); x += ff(norm(x))`` (src/model/cpu_llama.cpp:62-98), ``parallel`` is
     ``h = norm(x); x += mixer(h) + ff(h)`` (one norm, both sublayers read its output).  A block whose
     arrangement has no feed-forward, or no second norm, leaves those fields ``None``.
+    ``streams`` is the pre-norm order over several residual streams: each sublayer is joined to
+    them by a connection part (``mixer_connection``, ``feed_forward_connection``), which reads a
+    weighted sum of the streams for the norm and rewrites all streams from the sublayer's output.
     """
 
     arrangement: str
@@ -49,6 +52,8 @@ class BlockSpec:
     mixer: PartSpec
     feed_forward_norm: Optional[PartSpec] = None
     feed_forward: Optional[PartSpec] = None
+    mixer_connection: Optional[PartSpec] = None
+    feed_forward_connection: Optional[PartSpec] = None
 
 
 @dataclasses.dataclass(frozen=True)
@@ -79,10 +84,18 @@ class ModelSpec:
     schedule: Tuple[ScheduleEntry, ...]
     final_norm: PartSpec
     lm_head: PartSpec
+    # residual streams per token (1: one residual row).  With more, every block is of the
+    # ``streams`` arrangement, the embedding fills all of them and the final norm reads their sum.
+    streams: int = 1
 
     def validate(self) -> None:
         if not self.blocks or not self.schedule:
             raise ValueError("a model needs at least one block and one schedule entry")
+        if self.streams < 1:
+            raise ValueError("a model has at least one residual stream")
+        if self.streams > 1 and any(block.arrangement != "streams" for block in self.blocks):
+            raise ValueError("with several residual streams every block is of the 'streams' "
+                             "arrangement")
         for index, entry in enumerate(self.schedule):
             if not 0 <= entry.block < len(self.blocks):
                 raise ValueError(f"schedule entry {index} names block {entry.block}, "

@@ -24,6 +24,9 @@ CSRC = os.path.dirname(os.path.abspath(__file__))
 SOURCES = (
     "hx_elementwise.cu",
     "hx_short_conv.cu",
+    "hx_streams.cu",
+    "hx_recurrent.cu",
+    "hx_rotary_norm.cu",
     "hx_gemm_simt.cu",
     "hx_gemm_tc.cu",
     "hx_attention.cu",

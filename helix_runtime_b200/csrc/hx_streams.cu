@@ -1,0 +1,262 @@
+// Residual streams (hyper-connections), the sums around them, and the biased activation of a
+// plain feed-forward.
+//
+// A model with S residual streams keeps, per token, S rows of the model's width next to each
+// other: X[token][s][c], float32.  A sublayer reads a weighted sum of them,
+//
+//     u[c] = sum_s a[s] X[s][c],        h = u / sqrt(mean(u^2) + eps) * w[c],
+//
+// and, once it has produced y (float32, the sublayer's output before any sum), all streams
+// are rewritten at once from the old ones:
+//
+//     X'[r][c] = sum_s M[s][r] X[s][c] + b[r] * scale[c] * y[c].
+//
+// S = 1 with a = M = b = 1 is the ordinary residual sum with a per-channel layer scale.  All
+// of it is float32; only h is rounded to the compute type.
+#include "hx_common.cuh"
+
+namespace {
+
+constexpr int MAX_STREAMS = 16;
+
+// ------------------------------------------------------------------ spread the embedding
+
+__global__ void streams_spread_kernel(const float* __restrict__ x, float* __restrict__ streams,
+                                      int hidden, int count, size_t total) {
+  hx_pdl_prologue();
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t token = i / hidden;
+  const int c = static_cast<int>(i - token * hidden);
+  const float v = x[i];
+  float* row = streams + token * static_cast<size_t>(count) * hidden + c;
+  for (int s = 0; s < count; ++s) row[static_cast<size_t>(s) * hidden] = v;
+}
+
+// ------------------------------------------------------------- weighted read, RMS norm
+
+// One block per output row.  `rows` gathers (the final norm runs on the wanted rows only);
+// `clear`, when given, is the float32 row [hidden] that the sublayer will sum its output into:
+// it is zeroed here (row index = the token, not the gathered one).
+template <typename TOut>
+__global__ __launch_bounds__(256) void streams_read_norm_kernel(
+    const float* __restrict__ streams, const float* __restrict__ read, int count,
+    const float* __restrict__ weight, TOut* __restrict__ out, float* __restrict__ clear,
+    const int* __restrict__ rows, int hidden, float eps) {
+  __shared__ float scratch[32];
+  __shared__ float a[MAX_STREAMS];
+  if (threadIdx.x < count) a[threadIdx.x] = read != nullptr ? read[threadIdx.x] : 1.0f;
+  hx_pdl_prologue();
+  __syncthreads();
+  const int out_row = blockIdx.x;
+  const int in_row = rows != nullptr ? rows[out_row] : out_row;
+  const float* base = streams + static_cast<size_t>(in_row) * count * hidden;
+  float sum = 0.0f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float u = 0.0f;
+    for (int s = 0; s < count; ++s) u = fmaf(a[s], base[static_cast<size_t>(s) * hidden + c], u);
+    sum = fmaf(u, u, sum);
+  }
+  const float total = hx_block_sum(sum, scratch);
+  const float inverse = 1.0f / sqrtf(total / static_cast<float>(hidden) + eps);
+  TOut* yr = out + static_cast<size_t>(out_row) * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float u = 0.0f;
+    for (int s = 0; s < count; ++s) u = fmaf(a[s], base[static_cast<size_t>(s) * hidden + c], u);
+    yr[c] = hx_from_float<TOut>(u * inverse * weight[c]);
+    if (clear != nullptr) clear[static_cast<size_t>(out_row) * hidden + c] = 0.0f;
+  }
+}
+
+// ---------------------------------------------------------------- rewrite all streams
+
+__global__ __launch_bounds__(256) void streams_write_kernel(
+    float* __restrict__ streams, const float* __restrict__ y, const float* __restrict__ mixing,
+    const float* __restrict__ write, const float* __restrict__ scale, int count, int hidden,
+    size_t total) {
+  __shared__ float m[MAX_STREAMS * MAX_STREAMS];
+  __shared__ float b[MAX_STREAMS];
+  for (int i = threadIdx.x; i < count * count; i += blockDim.x)
+    m[i] = mixing != nullptr ? mixing[i] : 1.0f;
+  if (threadIdx.x < count) b[threadIdx.x] = write != nullptr ? write[threadIdx.x] : 1.0f;
+  hx_pdl_prologue();
+  __syncthreads();
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t token = i / hidden;
+  const int c = static_cast<int>(i - token * hidden);
+  float* row = streams + token * static_cast<size_t>(count) * hidden + c;
+  float old[MAX_STREAMS];
+#pragma unroll
+  for (int s = 0; s < MAX_STREAMS; ++s)
+    if (s < count) old[s] = row[static_cast<size_t>(s) * hidden];
+  const float add = (scale != nullptr ? scale[c] : 1.0f) * y[i];
+#pragma unroll
+  for (int r = 0; r < MAX_STREAMS; ++r) {
+    if (r < count) {
+      float v = 0.0f;
+#pragma unroll
+      for (int s = 0; s < MAX_STREAMS; ++s)
+        if (s < count) v = fmaf(m[s * count + r], old[s], v);
+      row[static_cast<size_t>(r) * hidden] = fmaf(b[r], add, v);
+    }
+  }
+}
+
+// ------------------------------------------------- sums of scaled rows, bias, activation
+
+// x[t][c] += sum_i scale[i] * source_i[t][c]; the sources (float32 accumulators of the
+// sublayers that ran side by side) are zeroed as they are read.
+struct ScaledSources {
+  float* source[4];
+  float scale[4];
+  int count;
+};
+
+__global__ void scaled_sum_kernel(float* __restrict__ x, ScaledSources sources, size_t total) {
+  hx_pdl_prologue();
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  float v = x[i];
+  for (int k = 0; k < sources.count; ++k) {
+    v = fmaf(sources.scale[k], sources.source[k][i], v);
+    sources.source[k][i] = 0.0f;
+  }
+  x[i] = v;
+}
+
+__global__ void add_bias_kernel(float* __restrict__ x, const float* __restrict__ bias, int width,
+                                size_t total) {
+  hx_pdl_prologue();
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  x[i] += bias[i % width];
+}
+
+enum BiasedActivation : int { ACT_XIELU = 0, ACT_TANH = 1 };
+
+// xIELU with its two constants already passed through softplus (ap = softplus(p),
+// aq = 1/2 + softplus(q)): z > 0: ap z^2 + z/2; z <= 0: aq (exp(z) - 1 - z) + z/2.
+__device__ __forceinline__ float xielu(float z, float ap, float aq) {
+  if (z > 0.0f) return fmaf(ap * z, z, 0.5f * z);
+  return fmaf(aq, expm1f(z) - z, 0.5f * z);
+}
+
+// out[t][c] = f(in[t][c] + bias[c]); `in` float32 (a product's sums), `out` the compute type.
+template <typename TOut>
+__global__ void biased_activation_kernel(const float* __restrict__ in, int ld_in,
+                                         const float* __restrict__ bias, TOut* __restrict__ out,
+                                         int ld_out, int width, size_t total, int activation,
+                                         float p0, float p1) {
+  hx_pdl_prologue();
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t token = i / width;
+  const int c = static_cast<int>(i - token * width);
+  float z = in[token * ld_in + c];
+  if (bias != nullptr) z += bias[c];
+  const float v = activation == ACT_TANH ? tanhf(z) : xielu(z, p0, p1);
+  out[token * ld_out + c] = hx_from_float<TOut>(v);
+}
+
+inline unsigned blocks_for(size_t total, int threads) {
+  return static_cast<unsigned>((total + threads - 1) / threads);
+}
+
+}  // namespace
+
+HX_API int hx_streams_spread(const float* x, float* streams, int tokens, int hidden, int count,
+                             cudaStream_t stream) {
+  HX_REQUIRE(tokens >= 0 && hidden > 0 && count >= 1, "hx_streams_spread: bad sizes");
+  if (tokens == 0) return HX_OK;
+  const size_t total = static_cast<size_t>(tokens) * hidden;
+  hx_launch(streams_spread_kernel, blocks_for(total, 256), 256, 0, stream, x, streams, hidden,
+            count, total);
+  HX_CHECK_LAUNCH("hx_streams_spread");
+  return HX_OK;
+}
+
+HX_API int hx_streams_read_norm(const float* streams, const float* read, int count,
+                                const float* weight, void* out, int out_dtype, float* clear,
+                                const int* rows, int n_rows, int hidden, float eps,
+                                cudaStream_t stream) {
+  HX_REQUIRE(n_rows >= 0 && hidden > 0, "hx_streams_read_norm: bad sizes");
+  HX_REQUIRE(count >= 1 && count <= MAX_STREAMS, "hx_streams_read_norm: 1 to %d streams",
+             MAX_STREAMS);
+  HX_REQUIRE(eps > 0.0f, "hx_streams_read_norm: eps must be positive");
+  if (n_rows == 0) return HX_OK;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (out_dtype == HX_F32) {
+    hx_launch(streams_read_norm_kernel<float>, n_rows, threads, 0, stream, streams, read, count,
+              weight, static_cast<float*>(out), clear, rows, hidden, eps);
+  } else if (out_dtype == HX_BF16) {
+    hx_launch(streams_read_norm_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, streams, read,
+              count, weight, static_cast<__nv_bfloat16*>(out), clear, rows, hidden, eps);
+  } else {
+    HX_REQUIRE(false, "hx_streams_read_norm: unknown dtype %d", out_dtype);
+  }
+  HX_CHECK_LAUNCH("hx_streams_read_norm");
+  return HX_OK;
+}
+
+HX_API int hx_streams_write(float* streams, const float* y, const float* mixing,
+                            const float* write, const float* scale, int count, int tokens,
+                            int hidden, cudaStream_t stream) {
+  HX_REQUIRE(tokens >= 0 && hidden > 0, "hx_streams_write: bad sizes");
+  HX_REQUIRE(count >= 1 && count <= MAX_STREAMS, "hx_streams_write: 1 to %d streams", MAX_STREAMS);
+  if (tokens == 0) return HX_OK;
+  const size_t total = static_cast<size_t>(tokens) * hidden;
+  hx_launch(streams_write_kernel, blocks_for(total, 256), 256, 0, stream, streams, y, mixing,
+            write, scale, count, hidden, total);
+  HX_CHECK_LAUNCH("hx_streams_write");
+  return HX_OK;
+}
+
+HX_API int hx_scaled_sum(float* x, float* const* sources, const float* scales, int count,
+                         int tokens, int width, cudaStream_t stream) {
+  HX_REQUIRE(count >= 1 && count <= 4, "hx_scaled_sum: 1 to 4 sources");
+  HX_REQUIRE(tokens >= 0 && width > 0, "hx_scaled_sum: bad sizes");
+  if (tokens == 0) return HX_OK;
+  ScaledSources packed;
+  packed.count = count;
+  for (int i = 0; i < count; ++i) {
+    packed.source[i] = sources[i];
+    packed.scale[i] = scales[i];
+  }
+  const size_t total = static_cast<size_t>(tokens) * width;
+  hx_launch(scaled_sum_kernel, blocks_for(total, 256), 256, 0, stream, x, packed, total);
+  HX_CHECK_LAUNCH("hx_scaled_sum");
+  return HX_OK;
+}
+
+HX_API int hx_add_bias(float* x, const float* bias, int tokens, int width, cudaStream_t stream) {
+  HX_REQUIRE(tokens >= 0 && width > 0, "hx_add_bias: bad sizes");
+  if (tokens == 0) return HX_OK;
+  const size_t total = static_cast<size_t>(tokens) * width;
+  hx_launch(add_bias_kernel, blocks_for(total, 256), 256, 0, stream, x, bias, width, total);
+  HX_CHECK_LAUNCH("hx_add_bias");
+  return HX_OK;
+}
+
+HX_API int hx_biased_activation(const float* in, int ld_in, const float* bias, void* out,
+                                int ld_out, int out_dtype, int tokens, int width, int activation,
+                                float p0, float p1, cudaStream_t stream) {
+  HX_REQUIRE(tokens >= 0 && width > 0 && ld_in >= width && ld_out >= width,
+             "hx_biased_activation: bad sizes");
+  HX_REQUIRE(activation == ACT_XIELU || activation == ACT_TANH,
+             "hx_biased_activation: unknown activation %d", activation);
+  if (tokens == 0) return HX_OK;
+  const size_t total = static_cast<size_t>(tokens) * width;
+  if (out_dtype == HX_F32) {
+    hx_launch(biased_activation_kernel<float>, blocks_for(total, 256), 256, 0, stream, in, ld_in,
+              bias, static_cast<float*>(out), ld_out, width, total, activation, p0, p1);
+  } else if (out_dtype == HX_BF16) {
+    hx_launch(biased_activation_kernel<__nv_bfloat16>, blocks_for(total, 256), 256, 0, stream, in,
+              ld_in, bias, static_cast<__nv_bfloat16*>(out), ld_out, width, total, activation, p0,
+              p1);
+  } else {
+    HX_REQUIRE(false, "hx_biased_activation: unknown dtype %d", out_dtype);
+  }
+  HX_CHECK_LAUNCH("hx_biased_activation");
+  return HX_OK;
+}

@@ -65,6 +65,9 @@ def load_model(model_dir: str, dtype: Union[str, torch.dtype] = "bfloat16",
     document, source = open_model(model_dir)
     architecture = architecture_for(document)
     config = architecture.config_from_dict(document)
+    if architecture.sizes_from_checkpoint is not None:
+        config = architecture.sizes_from_checkpoint(
+            config, {name: tuple(source.record(name).shape) for name in source.names()})
     model = DecoderModel(architecture.build_spec(config))
     model.config = config
     tensors = load_tensors(source, model.tensor_requests(), dtype, device)

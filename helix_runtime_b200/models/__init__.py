@@ -1,6 +1,8 @@
-from . import llama, rekasun  # noqa: F401  (register the architectures)
+from . import llama, rekasun, zuzadra  # noqa: F401  (register the architectures)
 from .decoder import Block, DecoderModel, register_arrangement
 from .llama import build_llama_spec
 from .rekasun import build_rekasun_spec
+from .zuzadra import build_zuzadra_spec
 
-__all__ = ["Block", "DecoderModel", "build_llama_spec", "build_rekasun_spec", "register_arrangement"]
+__all__ = ["Block", "DecoderModel", "build_llama_spec", "build_rekasun_spec",
+           "build_zuzadra_spec", "register_arrangement"]

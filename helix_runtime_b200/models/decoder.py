@@ -59,6 +59,26 @@ def _parallel(block: "Block", ctx: StepContext, cache: LayerCache, residual: tor
 register_arrangement("parallel", _parallel)
 
 
+def _streams(block: "Block", ctx: StepContext, cache: LayerCache, residual: torch.Tensor,
+             normed: torch.Tensor) -> None:
+    # residual holds the model's streams side by side per token.  Per sublayer: the connection
+    # reads their weighted sum through the norm and clears `output`; the sublayer sums its
+    # result into `output`; the connection rewrites all streams from the old ones and `output`.
+    output = ctx.workspace.get("model.sublayer_output", (ctx.capacity, block.hidden_size),
+                               torch.float32)
+    block.mixer_connection.read_normed(ctx, block.mixer_norm, residual, normed, output)
+    block.mixer.forward(ctx, cache, normed, output)
+    block.mixer_connection.write_back(ctx, residual, output)
+    if block.feed_forward is not None:
+        block.feed_forward_connection.read_normed(ctx, block.feed_forward_norm, residual, normed,
+                                                  output)
+        block.feed_forward.forward(ctx, normed, output)
+        block.feed_forward_connection.write_back(ctx, residual, output)
+
+
+register_arrangement("streams", _streams)
+
+
 class Block:
     """One decoder layer: its parts, and the arrangement that runs them."""
 
@@ -70,7 +90,13 @@ class Block:
         if (spec.feed_forward is None) != (spec.feed_forward_norm is None) \
                 and spec.arrangement == "pre_norm":
             raise ValueError("a pre_norm block has a feed-forward with its norm, or neither")
+        if spec.arrangement == "streams" and (
+                spec.mixer_connection is None or
+                (spec.feed_forward is not None and (spec.feed_forward_connection is None
+                                                    or spec.feed_forward_norm is None))):
+            raise ValueError("a streams block joins every sublayer with a connection and a norm")
         self.arrangement = spec.arrangement
+        self.hidden_size = hidden_size
         self._run = run
         self.mixer_norm: Norm = build_part("norm", spec.mixer_norm, hidden_size)
         self.mixer: Mixer = build_part("mixer", spec.mixer, hidden_size)
@@ -78,9 +104,14 @@ class Block:
             build_part("norm", spec.feed_forward_norm, hidden_size)
         self.feed_forward: Optional[FeedForward] = None if spec.feed_forward is None else \
             build_part("feed_forward", spec.feed_forward, hidden_size)
+        self.mixer_connection = None if spec.mixer_connection is None else \
+            build_part("connection", spec.mixer_connection, hidden_size)
+        self.feed_forward_connection = None if spec.feed_forward_connection is None else \
+            build_part("connection", spec.feed_forward_connection, hidden_size)
 
     def parts(self):
-        return tuple(part for part in (self.mixer_norm, self.mixer, self.feed_forward_norm,
+        return tuple(part for part in (self.mixer_norm, self.mixer_connection, self.mixer,
+                                       self.feed_forward_norm, self.feed_forward_connection,
                                        self.feed_forward) if part is not None)
 
     def forward(self, ctx: StepContext, cache: LayerCache, residual: torch.Tensor,
@@ -95,6 +126,7 @@ class DecoderModel:
         self.hidden_size = spec.hidden_size
         self.vocab_size = spec.vocab_size
         self.max_positions = spec.max_positions
+        self.streams = spec.streams
         self.embedding = build_part("embedding", spec.embedding, spec.hidden_size)
         self.blocks: List[Block] = [Block(block, spec.hidden_size) for block in spec.blocks]
         self.schedule = spec.schedule
@@ -192,11 +224,21 @@ class DecoderModel:
         """Run the step's tokens; return logits ``[n_want, vocab]`` float32 for the flattened
         token indices in ``want_rows`` (device int32), or None when nothing is wanted."""
         h = self.hidden_size
-        residual = ctx.workspace.get("model.residual", (ctx.capacity, h), torch.float32)
+        # with several residual streams a token's streams lie side by side in its row
+        residual = ctx.workspace.get("model.residual", (ctx.capacity, self.streams * h),
+                                     torch.float32)
         normed = ctx.workspace.get("model.normed", (ctx.capacity, h), ctx.dtype)
-        self.embedding.forward(ctx, residual)
         embedded = None
+        if self.streams > 1:
+            # every stream starts as the embedding's output
+            first = ctx.workspace.get("model.embedded", (ctx.capacity, h), torch.float32)
+            self.embedding.forward(ctx, first)
+            ops.streams_spread(first, residual, ctx.n_tokens, self.streams)
+        else:
+            self.embedding.forward(ctx, residual)
         if any(entry.add_embedding for entry in self.schedule):
+            if self.streams > 1:
+                raise ValueError("adding the embedding back in is defined for one residual stream")
             # the embedding's output is kept for the entries that add it back in
             embedded = ctx.workspace.get("model.embedded", (ctx.capacity, h), torch.float32)
             self.embedding.forward(ctx, embedded)
@@ -205,11 +247,18 @@ class DecoderModel:
                 ops.add_rows(residual, embedded, ctx.n_tokens)
             self.blocks[entry.block].forward(ctx, self.layer_cache(cache, index), residual, normed)
             if self.after_entry is not None:
-                self.after_entry(index, residual[:ctx.n_tokens])
+                rows = residual[:ctx.n_tokens]
+                self.after_entry(index, rows if self.streams == 1 else
+                                 rows.view(ctx.n_tokens, self.streams, h).sum(dim=1))
         if n_want == 0:
             return None
         wanted = ctx.workspace.get("model.wanted", (ctx.capacity, h), ctx.dtype)
         logits = ctx.workspace.get("model.logits", (ctx.capacity, self.vocab_size), torch.float32)
-        self.final_norm.forward(ctx, residual, wanted, rows=want_rows, n_rows=n_want)
+        if self.streams > 1:
+            # the norm of the sum of the streams
+            self.final_norm.forward_streams(ctx, residual, self.streams, None, wanted,
+                                            rows=want_rows, n_rows=n_want)
+        else:
+            self.final_norm.forward(ctx, residual, wanted, rows=want_rows, n_rows=n_want)
         self.lm_head.forward(ctx, wanted, logits, n_want)
         return logits[:n_want]

@@ -37,6 +37,7 @@ FLAG_BAD_POSITION = 16
 _c_int = ctypes.c_int
 _c_ptr = ctypes.c_void_p
 _c_float = ctypes.c_float
+_c_longlong = ctypes.c_longlong
 
 _lock = threading.Lock()
 _library: Optional[ctypes.CDLL] = None
@@ -126,6 +127,41 @@ def _declare(library: ctypes.CDLL) -> None:
     library.hx_feed_tokens.restype = _c_int
     library.hx_bounded_wait_check.argtypes = [_c_int, _c_int, _c_ptr, _c_ptr, _c_ptr]
     library.hx_bounded_wait_check.restype = _c_int
+    library.hx_streams_spread.argtypes = [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr]
+    library.hx_streams_read_norm.argtypes = [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr,
+                                             _c_ptr, _c_int, _c_int, _c_float, _c_ptr]
+    library.hx_streams_write.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
+                                         _c_int, _c_ptr]
+    library.hx_scaled_sum.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr]
+    library.hx_add_bias.argtypes = [_c_ptr, _c_ptr, _c_int, _c_int, _c_ptr]
+    library.hx_biased_activation.argtypes = [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
+                                             _c_int, _c_int, _c_float, _c_float, _c_ptr]
+    library.hx_causal_filter.argtypes = [_c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr,
+                                         _c_ptr, _c_longlong, _c_int, _c_int, _c_int, _c_int, _c_ptr,
+                                         _c_ptr, _c_ptr, _c_ptr]
+    library.hx_state_space_scan.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int,
+                                            _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_longlong, _c_ptr,
+                                            _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                            _c_ptr]
+    library.hx_token_shift.argtypes = [_c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_longlong,
+                                       _c_ptr, _c_longlong, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr,
+                                       _c_ptr]
+    library.hx_outer_product_scan.argtypes = [_c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int,
+                                              _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_longlong,
+                                              _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr]
+    library.hx_gated_group_norm.argtypes = [_c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr,
+                                            _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr]
+    library.hx_norm_rotary_append.argtypes = [
+        _c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr,
+        _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_float, _c_int, _c_int, _c_int, _c_int,
+        _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr]
+    library.hx_rotate_back.argtypes = [_c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
+                                       _c_int, _c_int, _c_ptr]
+    for name in ("hx_streams_spread", "hx_streams_read_norm", "hx_streams_write", "hx_scaled_sum",
+                 "hx_add_bias", "hx_biased_activation", "hx_causal_filter", "hx_state_space_scan",
+                 "hx_token_shift", "hx_outer_product_scan", "hx_gated_group_norm",
+                 "hx_norm_rotary_append", "hx_rotate_back"):
+        getattr(library, name).restype = _c_int
     for name in ("hx_embed", "hx_rmsnorm", "hx_swiglu", "hx_rope_append", "hx_gemm_simt",
                  "hx_gemm_tc", "hx_gemm_tc_supports", "hx_gemm_tc_token_tile",
                  "hx_paged_attention", "hx_argmax", "hx_sample", "hx_embed_scaled",
@@ -538,6 +574,248 @@ def prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
     else:
         _check(lib().hx_prefill_attention_windowed(*arguments, int(window), int(keep_first),
                                                    _ptr(status), _stream()))
+
+
+# ------------------------------------------------------------ residual streams, biased sums
+
+def streams_spread(x: torch.Tensor, streams: torch.Tensor, tokens: int, count: int) -> None:
+    """streams[t, s] = x[t] for every stream s; ``streams`` is ``[rows, count * hidden]``."""
+    _need(x, torch.float32, "x")
+    _need(streams, torch.float32, "streams")
+    hidden = x.shape[1]
+    assert x.is_contiguous() and streams.is_contiguous() and streams.shape[1] == count * hidden
+    _check(lib().hx_streams_spread(x.data_ptr(), streams.data_ptr(), tokens, hidden, count,
+                                   _stream()))
+
+
+def streams_read_norm(streams: torch.Tensor, read: Optional[torch.Tensor], count: int,
+                      weight: torch.Tensor, out: torch.Tensor, eps: float, n_rows: int,
+                      clear: Optional[torch.Tensor] = None,
+                      rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = rmsnorm(sum_s read[s] * streams[r', s]) * weight with r' = rows[r] or r
+    (``read`` None: every stream counts once).  ``clear`` (float32 ``[rows, hidden]``): its
+    first ``n_rows`` rows are zeroed, for the sublayer to sum its output into."""
+    _need(streams, torch.float32, "streams")
+    _need(weight, torch.float32, "weight")
+    hidden = weight.shape[0]
+    assert streams.is_contiguous() and out.is_contiguous() and out.shape[1] == hidden
+    assert streams.shape[1] == count * hidden
+    if read is not None:
+        _need(read, torch.float32, "read")
+        assert read.numel() == count
+    if clear is not None:
+        _need(clear, torch.float32, "clear")
+        assert clear.is_contiguous() and clear.shape[1] == hidden and rows is None
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+    _check(lib().hx_streams_read_norm(streams.data_ptr(), _ptr(read), count, weight.data_ptr(),
+                                      out.data_ptr(), dtype_code(out.dtype), _ptr(clear),
+                                      _ptr(rows), n_rows, hidden, float(eps), _stream()))
+
+
+def streams_write(streams: torch.Tensor, y: torch.Tensor, mixing: Optional[torch.Tensor],
+                  write: Optional[torch.Tensor], scale: Optional[torch.Tensor], count: int,
+                  tokens: int) -> None:
+    """streams[t, r] = sum_s mixing[s, r] * streams[t, s] + write[r] * scale * y[t], all streams
+    at once from the old ones (``mixing``, ``write`` None: ones; ``scale`` None: one)."""
+    _need(streams, torch.float32, "streams")
+    _need(y, torch.float32, "y")
+    hidden = y.shape[1]
+    assert streams.is_contiguous() and y.is_contiguous() and streams.shape[1] == count * hidden
+    for name, tensor, size in (("mixing", mixing, count * count), ("write", write, count),
+                               ("scale", scale, hidden)):
+        if tensor is not None:
+            _need(tensor, torch.float32, name)
+            assert tensor.is_contiguous() and tensor.numel() == size
+    _check(lib().hx_streams_write(streams.data_ptr(), y.data_ptr(), _ptr(mixing), _ptr(write),
+                                  _ptr(scale), count, tokens, hidden, _stream()))
+
+
+def scaled_sum(x: torch.Tensor, sources: Sequence[torch.Tensor], scales: Sequence[float],
+               tokens: int) -> None:
+    """x[:tokens] += sum_i scales[i] * sources[i][:tokens]; the sources' rows are zeroed."""
+    _need(x, torch.float32, "x")
+    width = x.shape[1]
+    for source in sources:
+        _need(source, torch.float32, "source")
+        assert source.is_contiguous() and source.shape[1] == width and source.shape[0] >= tokens
+    assert x.is_contiguous() and len(sources) == len(scales)
+    pointers = (ctypes.c_void_p * len(sources))(*[source.data_ptr() for source in sources])
+    factors = (ctypes.c_float * len(scales))(*[float(scale) for scale in scales])
+    _check(lib().hx_scaled_sum(x.data_ptr(), pointers, factors, len(sources), tokens, width,
+                               _stream()))
+
+
+def add_bias(x: torch.Tensor, bias: torch.Tensor, tokens: int) -> None:
+    """x[:tokens] += bias (float32)."""
+    _need(x, torch.float32, "x")
+    _need(bias, torch.float32, "bias")
+    assert x.is_contiguous() and bias.numel() == x.shape[1]
+    _check(lib().hx_add_bias(x.data_ptr(), bias.data_ptr(), tokens, x.shape[1], _stream()))
+
+
+ACT_XIELU = 0        # softplus(p) z^2 + z/2 above zero, (1/2 + softplus(q)) (e^z - 1 - z) + z/2 below
+ACT_TANH = 1
+
+
+def biased_activation(sums: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                      tokens: int, activation: int, p0: float = 0.0, p1: float = 0.0) -> None:
+    """out[:tokens] = f(sums[:tokens] + bias): ``sums`` float32, ``out`` the compute dtype.
+    For ACT_XIELU ``p0 = softplus(p)`` and ``p1 = 1/2 + softplus(q)``."""
+    _need(sums, torch.float32, "sums")
+    width = out.shape[1]
+    assert sums.shape[1] == width and sums.stride(-1) == 1 and out.stride(-1) == 1
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+        assert bias.numel() == width
+    _check(lib().hx_biased_activation(sums.data_ptr(), sums.stride(0), _ptr(bias), out.data_ptr(),
+                                      out.stride(0), dtype_code(out.dtype), tokens, width,
+                                      int(activation), float(p0), float(p1), _stream()))
+
+
+# ------------------------------------------------------------------------ recurrent mixers
+
+def causal_filter(raw: torch.Tensor, out: torch.Tensor, taps: torch.Tensor,
+                  bias: Optional[torch.Tensor], state: Optional[torch.Tensor], tokens: int,
+                  silu: bool, token_request: torch.Tensor, request_slot: torch.Tensor,
+                  request_start: torch.Tensor) -> None:
+    """out[t, c] = f(bias[c] + sum_j taps[c, j] * raw[t - (n - 1) + j, c]) along each request's
+    tokens, ``f`` silu or nothing; ``raw`` (a view of the filtered columns) and ``out`` in the
+    compute dtype.  ``state`` ``[slots, >= (n - 1) * channels]`` float32 holds each request's
+    last ``n - 1`` inputs and is updated."""
+    _need(taps, torch.float32, "taps")
+    channels, count = taps.shape
+    assert raw.dtype == out.dtype and raw.stride(-1) == 1 and out.stride(-1) == 1
+    assert raw.shape[1] == channels and out.shape[1] == channels and taps.is_contiguous()
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+    if count > 1:
+        _need(state, torch.float32, "state")
+        assert state.shape[1] >= (count - 1) * channels
+    _check(lib().hx_causal_filter(raw.data_ptr(), raw.stride(0), out.data_ptr(), out.stride(0),
+                                  dtype_code(out.dtype), taps.data_ptr(), _ptr(bias), _ptr(state),
+                                  0 if state is None else state.stride(0), count, channels,
+                                  1 if silu else 0, tokens, token_request.data_ptr(),
+                                  request_slot.data_ptr(), request_start.data_ptr(), _stream()))
+
+
+def state_space_scan(x: torch.Tensor, b: torch.Tensor, c: torch.Tensor, dt: torch.Tensor,
+                     dt_bias: torch.Tensor, a_log: torch.Tensor, skip: torch.Tensor,
+                     state: torch.Tensor, y: torch.Tensor, request_start: torch.Tensor,
+                     request_slot: torch.Tensor, requests: int, heads: int, width: int, rows: int,
+                     groups: int) -> None:
+    """The selective state-space recurrence over each request's tokens: per head
+    ``S = exp(-exp(a_log) d) S + d B x'``, ``y = S' C + skip x`` with ``d = softplus(dt +
+    dt_bias)``.  ``x`` ``[tokens, heads * width]``, ``b``, ``c`` ``[tokens, groups * rows]`` (views
+    of one buffer), ``dt`` ``[tokens, heads]``; ``state`` ``[slots, >= heads * rows * width]`` and
+    ``y`` ``[tokens, heads * width]`` float32."""
+    for name, tensor in (("dt_bias", dt_bias), ("a_log", a_log), ("skip", skip), ("state", state),
+                         ("y", y)):
+        _need(tensor, torch.float32, name)
+    assert x.dtype == b.dtype == c.dtype == dt.dtype
+    assert x.stride(0) == b.stride(0) == c.stride(0) and x.stride(-1) == 1 and dt.stride(-1) == 1
+    assert y.is_contiguous() and y.shape[1] == heads * width
+    assert state.shape[1] >= heads * rows * width
+    _check(lib().hx_state_space_scan(x.data_ptr(), b.data_ptr(), c.data_ptr(), x.stride(0),
+                                     dt.data_ptr(), dt.stride(0), dtype_code(x.dtype),
+                                     dt_bias.data_ptr(), a_log.data_ptr(), skip.data_ptr(),
+                                     state.data_ptr(), state.stride(0), y.data_ptr(),
+                                     request_start.data_ptr(), request_slot.data_ptr(), requests,
+                                     heads, width, rows, groups, _stream()))
+
+
+def token_shift(h: torch.Tensor, mu: torch.Tensor, out: torch.Tensor, state: torch.Tensor,
+                tokens: int, token_request: torch.Tensor, request_slot: torch.Tensor,
+                request_start: torch.Tensor) -> None:
+    """out[s, t] = h[t] + (h[t - 1] - h[t]) * mu[s]; the row before a request's first token of
+    this step is its ``state`` row (``[slots, >= hidden]`` float32), which becomes the step's
+    last row.  ``out`` is ``[mixes, rows, hidden]`` in the compute dtype."""
+    _need(mu, torch.float32, "mu")
+    _need(state, torch.float32, "state")
+    mixes, hidden = mu.shape
+    assert out.dtype == h.dtype and out.is_contiguous() and out.shape[0] == mixes
+    assert out.shape[2] == hidden and h.stride(-1) == 1 and mu.is_contiguous()
+    _check(lib().hx_token_shift(h.data_ptr(), h.stride(0), dtype_code(h.dtype), mu.data_ptr(), mixes,
+                                out.data_ptr(), out.stride(0), state.data_ptr(), state.stride(0),
+                                tokens, hidden, token_request.data_ptr(), request_slot.data_ptr(),
+                                request_start.data_ptr(), _stream()))
+
+
+def outer_product_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_log: torch.Tensor,
+                       w0: torch.Tensor, bonus: torch.Tensor, state: torch.Tensor, o: torch.Tensor,
+                       request_start: torch.Tensor, request_slot: torch.Tensor, requests: int,
+                       heads: int, dim: int) -> None:
+    """Per head ``o = (S + diag(bonus) k v')' r`` then ``S = diag(w) S + k v'`` with
+    ``w = exp(-exp(decay_log + w0))``; ``r``, ``k``, ``v`` ``[tokens, heads * dim]`` in the compute
+    dtype, ``decay_log`` and ``o`` float32, ``state`` ``[slots, >= heads * dim * dim]`` float32."""
+    for name, tensor in (("decay_log", decay_log), ("w0", w0), ("bonus", bonus), ("state", state),
+                         ("o", o)):
+        _need(tensor, torch.float32, name)
+    assert r.dtype == k.dtype == v.dtype and o.is_contiguous() and o.shape[1] == heads * dim
+    assert state.shape[1] >= heads * dim * dim
+    _check(lib().hx_outer_product_scan(r.data_ptr(), r.stride(0), k.data_ptr(), k.stride(0),
+                                       v.data_ptr(), v.stride(0), dtype_code(r.dtype),
+                                       decay_log.data_ptr(), decay_log.stride(0), w0.data_ptr(),
+                                       bonus.data_ptr(), state.data_ptr(), state.stride(0),
+                                       o.data_ptr(), request_start.data_ptr(),
+                                       request_slot.data_ptr(), requests, heads, dim, _stream()))
+
+
+def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
+                     tokens: int, groups: int, eps: float, gate_after: bool) -> None:
+    """Channels in ``groups`` equal parts, each over its own root mean square, times ``weight``;
+    the gate ``silu(gate)`` multiplies before the norm, or after it (``gate_after``).  ``y``
+    float32, ``gate`` and ``out`` in the compute dtype."""
+    _need(y, torch.float32, "y")
+    _need(weight, torch.float32, "weight")
+    channels = weight.numel()
+    assert gate.dtype == out.dtype and gate.stride(-1) == 1 and out.stride(-1) == 1
+    assert y.stride(-1) == 1 and y.shape[1] == channels
+    _check(lib().hx_gated_group_norm(y.data_ptr(), y.stride(0), gate.data_ptr(), gate.stride(0),
+                                     dtype_code(out.dtype), weight.data_ptr(), out.data_ptr(),
+                                     out.stride(0), tokens, channels, groups, float(eps),
+                                     1 if gate_after else 0, _stream()))
+
+
+# ------------------------------------------------- rotation from positions, normed heads
+
+ROTARY_LAYOUTS = {"interleaved": 0, "halves": 1}
+
+
+def norm_rotary_append(qkv: torch.Tensor, positions: torch.Tensor, token_request: torch.Tensor,
+                       request_table_row: torch.Tensor, block_tables: Optional[torch.Tensor],
+                       k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                       freq: torch.Tensor, value_freq: Optional[torch.Tensor],
+                       q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float,
+                       tokens: int, heads: int, kv_heads: int, head_dim: int, value_dim: int,
+                       row_dim: int, rotary_dim: int, layout: int, value_layout: int,
+                       page_size: int, num_pages: int, status: torch.Tensor,
+                       accum: Optional[torch.Tensor] = None) -> None:
+    """Per-head RMS norm of q and k (when the weights are given), rotation of their first
+    ``rotary_dim`` coordinates by ``position * freq``, rotation of the values over ``value_dim``
+    by ``position * value_freq`` (when given), queries back into ``qkv``, keys and values into
+    their pages.  ``accum`` as for :func:`rope_append`."""
+    _need(freq, torch.float32, "freq")
+    write = k_cache is not None
+    _check(lib().hx_norm_rotary_append(
+        qkv.data_ptr(), dtype_code(qkv.dtype), qkv.stride(0), _ptr(accum),
+        0 if accum is None else accum.stride(0), positions.data_ptr(), token_request.data_ptr(),
+        request_table_row.data_ptr(), _ptr(block_tables) if write else None,
+        block_tables.stride(0) if write else 0, _ptr(k_cache), _ptr(v_cache), 1 if write else 0,
+        freq.data_ptr(), _ptr(value_freq), _ptr(q_norm), _ptr(k_norm), float(eps), tokens, heads,
+        kv_heads, head_dim, value_dim, row_dim, rotary_dim, layout, value_layout, page_size,
+        num_pages, _ptr(status), _stream()))
+
+
+def rotate_back(rows: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor, tokens: int,
+                heads: int, row_dim: int, dims: int, layout: int) -> None:
+    """Every head of ``rows[:tokens]`` turned by minus its token's position over its first
+    ``dims`` coordinates, in place."""
+    _need(freq, torch.float32, "freq")
+    assert rows.stride(-1) == 1
+    _check(lib().hx_rotate_back(rows.data_ptr(), dtype_code(rows.dtype), rows.stride(0),
+                                positions.data_ptr(), freq.data_ptr(), tokens, heads, row_dim, dims,
+                                layout, _stream()))
 
 
 def argmax(logits: torch.Tensor, tokens_out: torch.Tensor, status: Optional[torch.Tensor]) -> None:

@@ -19,6 +19,9 @@ Optional mechanisms, each a parameter (absent: as if it did not exist):
   the last tap on the token's own value).  The last ``taps - 1`` projected values of a request
   are per-request state (``state_need``).  The filter kernel appends keys and values to the
   pages itself when the position encoding is ``none``.
+* rotated values and a query/key norm belong to the position encoding (``computed_rotary``):
+  when it has ``restore_values`` the attention output is handed to it before the gate and the
+  output projection.
 * ``output_gate`` (``"sigmoid"``): the concatenated heads are multiplied by
   ``sigmoid(g x)`` before the output projection (tensor ``g`` ``[heads*value_dim, hidden]``);
   with a filter the gate's projection is part of the fused product.
@@ -104,7 +107,8 @@ class PagedAttention(Mixer):
         if wide != self.head_dim or self.value_dim != self.head_dim:
             position = spec["position"]
             padded = build_part("position", PartSpec(position.kind,
-                                                     {**position.params, "row_dim": wide},
+                                                     {**position.params, "row_dim": wide,
+                                                      "value_dim": self.value_dim},
                                                      position.tensors), hidden_size)
             if getattr(padded, "row_dim", None) == wide:
                 self.position, self.row_dim = padded, wide
@@ -319,6 +323,9 @@ class PagedAttention(Mixer):
                                 ctx.status, request_start=ctx.request_start,
                                 skip_query_len=TENSOR_CORE_MIN_QUERY if tensor_cores else 0,
                                 arrivals=arrivals, keep_first=kept)
+        restore = getattr(self.position, "restore_values", None)
+        if restore is not None:
+            restore(ctx, context, self.heads)
         if self.gated:
             if self.fused_gate:
                 gate = gate_rows[:, self.qkv_size:]

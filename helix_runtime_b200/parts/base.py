@@ -210,12 +210,12 @@ class FeedForward(Part):
 # ------------------------------------------------------------------- registry
 
 _REGISTRY: Dict[Tuple[str, str], Callable[[PartSpec, int], Part]] = {}
-_FAMILIES = ("norm", "position", "mixer", "feed_forward", "embedding", "lm_head")
+_FAMILIES = ("norm", "position", "mixer", "feed_forward", "embedding", "lm_head", "connection")
 
 
 def register_part(family: str, kind: str, factory: Callable[[PartSpec, int], Part]) -> None:
     """Make ``kind`` buildable.  ``family`` is one of norm, position, mixer, feed_forward,
-    embedding, lm_head; ``factory(spec, hidden_size)`` returns the part."""
+    embedding, lm_head, connection; ``factory(spec, hidden_size)`` returns the part."""
     if family not in _FAMILIES:
         raise ValueError(f"unknown part family {family!r}; known: {', '.join(_FAMILIES)}")
     _REGISTRY[(family, kind)] = factory

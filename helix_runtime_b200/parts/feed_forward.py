@@ -6,9 +6,12 @@ the tanh approximation of GELU, ``z * sigmoid(2 c (z + a z^3))`` with ``c = sqrt
 ``[intermediate, hidden]`` and ``down`` ``[hidden, intermediate]``.  gate and up are
 fused into one ``[2I, H]`` matrix at load so that both products read the input once;
 on the tensor cores the gated activation is the epilogue of that product.
+
+:class:`DenseMlp` is the plain two-matrix feed-forward ``down(act(up(x) + b)) + b'``.
 """
 from __future__ import annotations
 
+import math
 from typing import List, Mapping, Optional
 
 import torch
@@ -57,4 +60,62 @@ class GatedMlp(FeedForward):
         project(act, self.w_down, residual, n, ops.EPI_ADD_F32, ctx.status, ctx.ordered_sums)
 
 
+class DenseMlp(FeedForward):
+    """``down(act(up(x) + b_up)) + b_down`` with biases on both projections (``bias``: False for
+    none).  ``activation`` ``xielu``: with the two numbers ``p, q`` of the tensor ``act``,
+    ``act(z) = softplus(p) z^2 + z/2`` for ``z > 0`` and ``(1/2 + softplus(q)) (exp(z) - 1 - z) +
+    z/2`` otherwise; the sums of the first product, the bias and the activation are float32,
+    one rounding into the compute dtype.  Tensors: ``up`` ``[intermediate, hidden]``, ``down``
+    ``[hidden, intermediate]``, ``up_bias``, ``down_bias``, ``act`` ``[2]``."""
+
+    def __init__(self, spec: PartSpec, hidden_size: int) -> None:
+        super().__init__(spec, hidden_size)
+        self.intermediate = int(spec["intermediate_size"])
+        activation = spec.get("activation", "xielu")
+        if activation != "xielu":
+            raise ValueError(f"activation {activation!r} has no kernel here; only 'xielu'")
+        self.bias = bool(spec.get("bias", True))
+        self.names = dict(spec.tensors)
+        self.w_up: Optional[Weight] = None
+        self.w_down: Optional[Weight] = None
+        self.up_bias: Optional[torch.Tensor] = None
+        self.down_bias: Optional[torch.Tensor] = None
+        self.constants = (0.0, 0.0)
+
+    def tensor_requests(self) -> List[TensorRequest]:
+        h, i = self.hidden_size, self.intermediate
+        requests = [TensorRequest(self.names["up"], (i, h)), TensorRequest(self.names["down"], (h, i)),
+                    TensorRequest(self.names["act"], (2,), role="scale")]
+        if self.bias:
+            requests += [TensorRequest(self.names["up_bias"], (i,), role="scale"),
+                         TensorRequest(self.names["down_bias"], (h,), role="scale")]
+        return requests
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], dtype, device) -> None:
+        self.w_up = Weight(tensors[self.names["up"]].to(device=device, dtype=dtype).contiguous())
+        self.w_down = Weight(tensors[self.names["down"]].to(device=device, dtype=dtype).contiguous())
+        if self.bias:
+            self.up_bias = tensors[self.names["up_bias"]].to(device=device, dtype=torch.float32).contiguous()
+            self.down_bias = tensors[self.names["down_bias"]].to(device=device, dtype=torch.float32).contiguous()
+        p, q = (float(v) for v in tensors[self.names["act"]].to(torch.float64).cpu())
+        softplus = lambda z: max(z, 0.0) + math.log1p(math.exp(-abs(z)))
+        self.constants = (softplus(p), 0.5 + softplus(q))
+
+    def weight_bytes(self) -> int:
+        return self.w_up.nbytes() + self.w_down.nbytes()
+
+    def forward(self, ctx: StepContext, x: torch.Tensor, residual: torch.Tensor) -> None:
+        n = ctx.n_tokens
+        sums = ctx.workspace.get(f"mlp.up/{self.intermediate}", (ctx.capacity, self.intermediate),
+                                 torch.float32)
+        act = ctx.workspace.get(f"mlp.act/{self.intermediate}", (ctx.capacity, self.intermediate),
+                                ctx.dtype)
+        project(x, self.w_up, sums, n, ops.EPI_STORE_F32, ctx.status)
+        ops.biased_activation(sums, self.up_bias, act, n, ops.ACT_XIELU, *self.constants)
+        if self.down_bias is not None:
+            ops.add_bias(residual, self.down_bias, n)
+        project(act, self.w_down, residual, n, ops.EPI_ADD_F32, ctx.status, ctx.ordered_sums)
+
+
 register_part("feed_forward", "gated_mlp", GatedMlp)
+register_part("feed_forward", "dense_mlp", DenseMlp)

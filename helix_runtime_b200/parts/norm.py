@@ -2,7 +2,9 @@
 LayerNorm: see :class:`LayerNorm`.
 
 Reads the float32 residual stream, computes in float32, writes the compute dtype.
-Parameters: ``eps``; tensors: ``weight`` ``[hidden]``.
+Parameters: ``eps``, ``one_plus`` (the weight is stored around zero and the row is multiplied
+by ``1 + w``; the sum is taken in float32 at load); tensors: ``weight`` ``[hidden]``.
+``forward_streams`` is the same norm on a weighted sum of several residual streams.
 """
 from __future__ import annotations
 
@@ -22,6 +24,7 @@ class RmsNorm(Norm):
         self.eps = float(spec["eps"])
         if not self.eps > 0.0:
             raise ValueError("RmsNorm eps must be positive")
+        self.one_plus = bool(spec.get("one_plus", False))
         self.weight_name = spec.tensors["weight"]
         self.weight: Optional[torch.Tensor] = None
 
@@ -29,7 +32,8 @@ class RmsNorm(Norm):
         return [TensorRequest(self.weight_name, (self.hidden_size,), role="scale")]
 
     def bind(self, tensors: Mapping[str, torch.Tensor], dtype, device) -> None:
-        self.weight = tensors[self.weight_name].to(device=device, dtype=torch.float32).contiguous()
+        weight = tensors[self.weight_name].to(device=device, dtype=torch.float32)
+        self.weight = (weight + 1.0 if self.one_plus else weight).contiguous()
 
     def weight_bytes(self) -> int:
         return self.hidden_size * 4
@@ -38,6 +42,16 @@ class RmsNorm(Norm):
                 rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> None:
         count = ctx.n_tokens if n_rows is None else n_rows
         ops.rmsnorm(x, self.weight, out[:count], self.eps, rows)
+
+    def forward_streams(self, ctx: StepContext, streams: torch.Tensor, count: int,
+                        read: Optional[torch.Tensor], out: torch.Tensor,
+                        clear: Optional[torch.Tensor] = None,
+                        rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> None:
+        """The norm of ``sum_s read[s] * streams[:, s]`` (``read`` None: the plain sum) for
+        ``streams`` ``[rows, count * hidden]``; ``clear``: a float32 buffer whose rows are zeroed
+        on the way (the sublayer sums its output into it)."""
+        ops.streams_read_norm(streams, read, count, self.weight, out, self.eps,
+                              ctx.n_tokens if n_rows is None else n_rows, clear=clear, rows=rows)
 
 
 class LayerNorm(Norm):

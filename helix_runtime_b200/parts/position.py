@@ -119,5 +119,100 @@ class NoPosition(PositionEncoding):
                         cache.num_pages, ctx.status, accum=accum)
 
 
+class ComputedRotary(PositionEncoding):
+    """Rotary encoding whose angles are computed from the position (no table, so no bound on
+    positions), with three optional companions in the same kernel.
+
+    Parameters: ``theta``, ``head_dim``, ``rotary_dim`` (default: all of the head; 0: none),
+    ``row_dim`` (default ``head_dim``), ``pairing`` (``half_split``: ``(m, m + rotary_dim/2)``,
+    the default; ``adjacent``: ``(2m, 2m + 1)``).  The angle of pair ``m`` at position ``p`` is
+    the float32 product ``p * f[m]`` with ``f[m] = theta^(-2m / rotary_dim)`` rounded to float32
+    once; sine and cosine are float32.
+
+    * ``qk_norm`` (with ``eps``): before the rotation every query and key head is divided by
+      its root mean square over ``head_dim`` and multiplied by the weight ``q_norm`` (keys:
+      ``k_norm``) ``[head_dim]``, one weight for all heads.
+    * ``rotate_values`` (with ``value_dim``; ``value_theta`` and ``value_pairing`` default to the
+      keys'): the value of position ``j`` is turned by ``j`` over all ``value_dim`` coordinates,
+      pair ``m`` by ``j * value_theta^(-2m / value_dim)``, and cached so; :meth:`restore_values`
+      turns a head's attention output at position ``i`` back by ``-i``.
+    """
+
+    def __init__(self, spec: PartSpec, hidden_size: int) -> None:
+        super().__init__(spec, hidden_size)
+        self.theta = float(spec["theta"])
+        self.head_dim = int(spec["head_dim"])
+        self.rotary_dim = int(spec.get("rotary_dim", self.head_dim))
+        self.row_dim = int(spec.get("row_dim", self.head_dim))
+        self.value_dim = int(spec.get("value_dim", self.head_dim))
+        if self.row_dim < max(self.head_dim, self.value_dim):
+            raise ValueError("row_dim must hold the head and its values")
+        pairing = spec.get("pairing", "half_split")
+        if pairing not in PAIRINGS:
+            raise ValueError(f"unknown rotary pairing {pairing!r}")
+        self.pairing = pairing
+        if self.rotary_dim % 2 or not 0 <= self.rotary_dim <= self.head_dim:
+            raise ValueError("rotary_dim must be even and at most head_dim")
+        if not self.theta > 0.0:
+            raise ValueError("rotary theta must be positive")
+        self.qk_norm = bool(spec.get("qk_norm", False))
+        self.eps = float(spec.get("eps", 0.0))
+        if self.qk_norm and not self.eps > 0.0:
+            raise ValueError("the query and key norm needs a positive eps")
+        self.rotate_values = bool(spec.get("rotate_values", False))
+        self.value_theta = float(spec.get("value_theta", self.theta))
+        value_pairing = spec.get("value_pairing", pairing)
+        if value_pairing not in PAIRINGS:
+            raise ValueError(f"unknown rotary pairing {value_pairing!r}")
+        self.value_pairing = value_pairing
+        if self.rotate_values and self.value_dim % 2:
+            raise ValueError("rotated values need an even value_dim")
+        self.names = dict(spec.tensors)
+        self.freq: Optional[torch.Tensor] = None
+        self.value_freq: Optional[torch.Tensor] = None
+        self.q_norm: Optional[torch.Tensor] = None
+        self.k_norm: Optional[torch.Tensor] = None
+
+    @staticmethod
+    def frequencies(theta: float, dims: int, device) -> torch.Tensor:
+        half = max(dims // 2, 1)
+        exponent = -2.0 * torch.arange(half, dtype=torch.float64) / float(max(dims, 1))
+        return torch.pow(torch.tensor(theta, dtype=torch.float64), exponent) \
+            .to(torch.float32).to(device).contiguous()
+
+    def tensor_requests(self):
+        if not self.qk_norm:
+            return []
+        from ..weights.loader import TensorRequest
+        return [TensorRequest(self.names["q_norm"], (self.head_dim,), role="scale"),
+                TensorRequest(self.names["k_norm"], (self.head_dim,), role="scale")]
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], dtype, device) -> None:
+        self.freq = self.frequencies(self.theta, self.rotary_dim, device)
+        if self.rotate_values:
+            self.value_freq = self.frequencies(self.value_theta, self.value_dim, device)
+        if self.qk_norm:
+            self.q_norm = tensors[self.names["q_norm"]].to(device=device, dtype=torch.float32).contiguous()
+            self.k_norm = tensors[self.names["k_norm"]].to(device=device, dtype=torch.float32).contiguous()
+
+    def apply(self, ctx: StepContext, cache: LayerCache, qkv: torch.Tensor, heads: int,
+              kv_heads: int, accum: Optional[torch.Tensor] = None) -> None:
+        write = cache.owns and cache.keys is not None
+        ops.norm_rotary_append(qkv, ctx.positions, ctx.token_request, ctx.request_slot,
+                               cache.block_tables, cache.keys if write else None,
+                               cache.values if write else None, self.freq, self.value_freq,
+                               self.q_norm, self.k_norm, self.eps, ctx.n_tokens, heads, kv_heads,
+                               self.head_dim, self.value_dim, self.row_dim, self.rotary_dim,
+                               PAIRINGS[self.pairing], PAIRINGS[self.value_pairing],
+                               cache.page_size, cache.num_pages, ctx.status, accum=accum)
+
+    def restore_values(self, ctx: StepContext, context: torch.Tensor, heads: int) -> None:
+        """Turn every head of the attention output back by its query's position (in place)."""
+        if self.rotate_values:
+            ops.rotate_back(context, ctx.positions, self.value_freq, ctx.n_tokens, heads,
+                            self.row_dim, self.value_dim, PAIRINGS[self.value_pairing])
+
+
 register_part("position", "rotary", RotaryEncoding)
+register_part("position", "computed_rotary", ComputedRotary)
 register_part("position", "none", NoPosition)
