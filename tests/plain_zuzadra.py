@@ -294,6 +294,19 @@ class PlainZuzadra:
             + list(range(loop["start"], loop["stop"])) * loop["times"] \
             + list(range(loop["stop"], count))
 
+    def logits(self, tokens) -> np.ndarray:
+        return self.forward(tokens).astype(np.float32)
+
+    def hidden_states(self, tokens) -> List[np.ndarray]:
+        """The residual (the sum of the streams) after every run of a layer."""
+        states: List[np.ndarray] = []
+        self.after_layer = lambda run, x: states.append(x.copy())
+        try:
+            self.forward(tokens)
+        finally:
+            self.after_layer = None
+        return states
+
     def forward(self, tokens) -> np.ndarray:
         """Logits ``[T, vocab]`` of one whole sequence from position 0."""
         tokens = np.asarray(tokens, dtype=np.int64)
