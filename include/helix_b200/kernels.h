@@ -108,6 +108,82 @@ int hx_short_conv_append(const void* raw, int ld_raw, const float* accum, int ld
                          int kv_heads, int head_dim, int total, int page_size, int num_pages,
                          int* status, cudaStream_t stream);
 
+/* ---- residual streams, sums around them, biased activation ------------------------------ */
+/* A token's `count` residual streams lie side by side: streams[token][s][hidden], float32. */
+int hx_streams_spread(const float* x, float* streams, int tokens, int hidden, int count,
+                      cudaStream_t stream);
+/* out[r] = rmsnorm(sum_s read[s] * streams[rows ? rows[r] : r][s]) * weight (read NULL: ones);
+ * clear (may be NULL): float32 rows [n_rows, hidden] that are zeroed */
+int hx_streams_read_norm(const float* streams, const float* read, int count, const float* weight,
+                         void* out, int out_dtype, float* clear, const int* rows, int n_rows,
+                         int hidden, float eps, cudaStream_t stream);
+/* streams[t][r] = sum_s mixing[s][r] * streams[t][s] + write[r] * scale[c] * y[t][c], all r at
+ * once from the old streams (mixing, write, scale NULL: ones) */
+int hx_streams_write(float* streams, const float* y, const float* mixing, const float* write,
+                     const float* scale, int count, int tokens, int hidden, cudaStream_t stream);
+/* x += sum_i scales[i] * sources[i] (host arrays of `count` <= 4); the sources are zeroed */
+int hx_scaled_sum(float* x, float* const* sources, const float* scales, int count, int tokens,
+                  int width, cudaStream_t stream);
+int hx_add_bias(float* x, const float* bias, int tokens, int width, cudaStream_t stream);
+/* out = f(in + bias); activation 0: xIELU with p0 = softplus(p), p1 = 1/2 + softplus(q)
+ * (z > 0: p0 z^2 + z/2; else p1 (exp(z) - 1 - z) + z/2); 1: tanh */
+int hx_biased_activation(const float* in, int ld_in, const float* bias, void* out, int ld_out,
+                         int out_dtype, int tokens, int width, int activation, float p0, float p1,
+                         cudaStream_t stream);
+
+/* ---- recurrent mixers ------------------------------------------------------------------ */
+/* Per-request state is float32, `state + slot * state_stride`, zero at admission. */
+/* out[t][c] = f(bias[c] + sum_j taps[c][j] * raw[t - (n - 1) + j][c]) along each request; the
+ * state holds the last n - 1 inputs [n - 1][channels]; silu != 0: f = silu */
+int hx_causal_filter(const void* raw, int ld_raw, void* out, int ld_out, int dtype,
+                     const float* taps_weight, const float* bias, float* state,
+                     long long state_stride, int taps, int channels, int silu, int tokens,
+                     const int* token_request, const int* request_slot, const int* request_start,
+                     cudaStream_t stream);
+/* per head: S = exp(-exp(a_log) d) S + d B x', y = S' C + skip x, d = softplus(dt + dt_bias);
+ * state [heads][rows][width]; y float32 [tokens][heads * width] */
+int hx_state_space_scan(const void* x, const void* b, const void* c, int ld, const void* dt,
+                        int ld_dt, int dtype, const float* dt_bias, const float* a_log,
+                        const float* skip, float* state, long long state_stride, float* y,
+                        const int* request_start, const int* request_slot, int requests, int heads,
+                        int width, int rows, int groups, cudaStream_t stream);
+/* out[s][t] = h[t] + (h[t-1] - h[t]) * mu[s]; the state row [hidden] is the previous step's
+ * last row and becomes this step's */
+int hx_token_shift(const void* h, int ld, int dtype, const float* mu, int mixes, void* out,
+                   long long mix_stride, float* state, long long state_stride, int tokens,
+                   int hidden, const int* token_request, const int* request_slot,
+                   const int* request_start, cudaStream_t stream);
+/* per head: o = (S + diag(bonus) k v')' r, then S = diag(w) S + k v', w = exp(-exp(decay_log +
+ * w0)); state [heads][dim][dim]; o float32 */
+int hx_outer_product_scan(const void* r, int ld_r, const void* k, int ld_k, const void* v,
+                          int ld_v, int dtype, const float* decay_log, int ld_decay,
+                          const float* w0, const float* bonus, float* state,
+                          long long state_stride, float* o, const int* request_start,
+                          const int* request_slot, int requests, int heads, int dim,
+                          cudaStream_t stream);
+/* channels in `groups` equal parts, each over its root mean square, times weight; the gate
+ * silu(gate) multiplies before the norm (gate_after 0) or after it (1) */
+int hx_gated_group_norm(const float* y, int ld_y, const void* gate, int ld_gate, int dtype,
+                        const float* weight, void* out, int ld_out, int tokens, int channels,
+                        int groups, float eps, int gate_after, cudaStream_t stream);
+
+/* ---- rotation from positions, normed heads, rotated values + cache append --------------- */
+/* heads are row_dim wide (head_dim / value_dim real coordinates); q_norm, k_norm (both or
+ * neither): per-head RMS norm before the rotation; freq [rotary_dim / 2]; value_freq
+ * [value_dim / 2] or NULL (values stored as projected); layout 0: pairs (2m, 2m+1), 1:
+ * (m, m + dims/2); accum as for hx_rope_append */
+int hx_norm_rotary_append(void* qkv, int dtype, int ld, float* accum, int ld_accum,
+                          const int* positions, const int* token_request,
+                          const int* request_table_row, const int* block_tables, int table_stride,
+                          void* k_cache, void* v_cache, int write_cache, const float* freq,
+                          const float* value_freq, const float* q_norm, const float* k_norm,
+                          float eps, int tokens, int heads, int kv_heads, int head_dim,
+                          int value_dim, int row_dim, int rotary_dim, int layout, int value_layout,
+                          int page_size, int num_pages, int* status, cudaStream_t stream);
+/* every head of rows[t] turned by minus positions[t] over its first `dims` coordinates */
+int hx_rotate_back(void* rows, int dtype, int ld, const int* positions, const float* freq,
+                   int tokens, int heads, int row_dim, int dims, int layout, cudaStream_t stream);
+
 /* ---- rotary encoding + cache append ---------------------------------------------------- */
 /* qkv row = [q heads | k heads | v heads]; pairing 0: pairs (2p, 2p+1), 1: (p, p + rotary/2).
  * accum != NULL: take the row from this float32 accumulator instead and clear it. */
