@@ -374,8 +374,39 @@ def rekasun_config(shape: dict, options):
                          max_positions=shape["max_position_embeddings"])
 
 
+def zuzadra_config(shape: dict, options):
+    """The Zuzadra design with the layer sizes of a Llama shape: the same width, feed-forward and
+    vocabulary; every third layer the parallel mixer (sliding-window attention with the shape's
+    heads beside a time-mixing layer of the model's width in heads of 64), the others
+    state-space layers of twice the width in heads of 64 with a state of 128; four residual
+    streams; no repeated stretch."""
+    import math
+
+    from helix_runtime_b200.config.rekasun import DenseMlpConfig
+    from helix_runtime_b200.config.zuzadra import (ParallelMixerConfig, StateSpaceMixerConfig,
+                                                   TimeMixConfig, WindowAttentionConfig,
+                                                   ZuzadraConfig, ZuzadraLayerConfig)
+    heads, dim, width = shape["num_attention_heads"], shape["head_dim"], shape["hidden_size"]
+    state_heads = 2 * width // 64
+    state_space = StateSpaceMixerConfig(heads=state_heads, vdim=64, state=128,
+                                        groups=8 if state_heads % 8 == 0 else 1, conv=4,
+                                        norm_groups=8 if state_heads % 8 == 0 else 1)
+    left = WindowAttentionConfig(heads=heads, kv_heads=options.kv_heads or heads, dim=dim, vdim=dim,
+                                 scale=1.0 / math.sqrt(dim), window=options.window,
+                                 rot_base=10000.0, rot_dims=dim // 2, rot_layout="halves")
+    parallel = ParallelMixerConfig(left=left, right=TimeMixConfig(heads=width // 64, dim=64, rank=64),
+                                   left_scale=0.5, right_scale=0.5)
+    mlp = DenseMlpConfig(shape["intermediate_size"])
+    layers = tuple(ZuzadraLayerConfig("parallel", parallel, mlp) if index % 3 == 2 else
+                   ZuzadraLayerConfig("mamba2", state_space, mlp)
+                   for index in range(shape["num_hidden_layers"]))
+    return ZuzadraConfig(vocab=shape["vocab_size"], width=width, norm_eps=shape["rms_norm_eps"],
+                         layers=layers, streams=4, max_positions=shape["max_position_embeddings"])
+
+
 def compare_designs(options, peaks, device) -> int:
-    """``--compare``: the Rekasun design beside the Llama design at equal layer sizes, a few
+    """``--compare``: the Rekasun design beside the Llama design at equal layer sizes
+    (``--compare zuzadra``: and the Zuzadra design beside both), a few
     layers (``--layers``, default 4) of every benchmark shape, random weights, bfloat16.
     Prefill: one prompt of 2,048 tokens through the step function, CUDA events over five
     repeats.  Decode: ``--batch`` (default 8) and 64 requests at a context of 1,536 through
@@ -443,6 +474,9 @@ def compare_designs(options, peaks, device) -> int:
                 2 * need.kv_heads * need.head_dim * 2
                 * (context if need.window is None else min(context, need.window + need.keep_first))
                 for need in kv.values())
+            # recurrent state is read and written once per request and step
+            step_bytes += batch * sum(2 * int(np.prod(need.shape)) * need.dtype.itemsize
+                                      for need in state.values())
             result[f"decode_b{batch}_ms"] = round(ms, 4)
             result[f"decode_b{batch}_tokens_per_s"] = round(batch / ms * 1e3, 1)
             result[f"decode_b{batch}_hbm_frac"] = round(step_bytes / (ms / 1e3) / 1e9
@@ -460,15 +494,19 @@ def compare_designs(options, peaks, device) -> int:
         shape = dict(SHAPES[name], num_hidden_layers=layers)
         row = {"hidden": shape["hidden_size"], "heads": shape["num_attention_heads"],
                "head_dim": shape["head_dim"], "intermediate": shape["intermediate_size"]}
-        for design, config in (("llama", LlamaConfig(**shape)),
-                               ("rekasun", rekasun_config(shape, options))):
+        designs = [("llama", LlamaConfig(**shape)), ("rekasun", rekasun_config(shape, options))]
+        if options.compare == "zuzadra":
+            designs.append(("zuzadra", zuzadra_config(shape, options)))
+        for design, config in designs:
             model = random_model(config, seed=0, dtype="bfloat16", device=device)
             row[design] = measure(model)
             del model
             torch.cuda.empty_cache()
         shapes[name] = row
     print(json.dumps({
-        "metric": "prefill and decode throughput, Rekasun design beside Llama design (bf16)",
+        "metric": "prefill and decode throughput, " + ("Zuzadra and " if options.compare == "zuzadra"
+                                                        else "") +
+                  "Rekasun design beside Llama design (bf16)",
         "layers": layers, "prefill_tokens": PREFILL_TOKENS, "decode_context": context,
         "rekasun": {"window": options.window, "keep_first": options.keep_first,
                     "taps": options.taps, "kv_heads": options.kv_heads or "as query heads"},
@@ -501,13 +539,15 @@ def main() -> int:
     parser.add_argument("--shape", choices=tuple(SHAPES), default="llama-2-7b",
                         help="layer sizes for --serving, --profile and --timeline (the contract "
                              "line is always the Llama-2-7B shape)")
-    parser.add_argument("--design", choices=("llama", "rekasun"), default="llama",
+    parser.add_argument("--design", choices=("llama", "rekasun", "zuzadra"), default="llama",
                         help="which decoder the layers of --shape are built as, for --profile "
                              "and --timeline (the contract line is always the Llama design)")
-    parser.add_argument("--compare", action="store_true",
+    parser.add_argument("--compare", nargs="?", const="rekasun", default=None,
+                        choices=("rekasun", "zuzadra"),
                         help="prefill and decode throughput of the Rekasun design beside the "
                              "Llama design at equal layer sizes (a few layers of each --shape), "
-                             "as one JSON line of its own")
+                             "as one JSON line of its own; '--compare zuzadra' adds the Zuzadra "
+                             "design as a third row")
     parser.add_argument("--window", type=int, default=1024,
                         help="--design rekasun / --compare: keys a position sees behind itself")
     parser.add_argument("--keep-first", type=int, default=64,
@@ -562,6 +602,8 @@ def main() -> int:
     config = LlamaConfig(**shape)
     if options.design == "rekasun":
         config = rekasun_config(shape, options)
+    elif options.design == "zuzadra":
+        config = zuzadra_config(shape, options)
     model = random_model(config, seed=0, dtype="bfloat16", device=device)
     rng = np.random.default_rng(0)
     out_dir = options.log_dir or tempfile.mkdtemp(prefix="helix_bench_")

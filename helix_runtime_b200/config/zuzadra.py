@@ -231,6 +231,36 @@ class ZuzadraConfig:
             layers.append(layer)
         return dataclasses.replace(self, layers=tuple(layers))
 
+    @staticmethod
+    def random_scale(name: str, shape: Tuple[int, ...]):
+        """What a model with random weights holds in its vectors and small tables (None: ones):
+        norm weights are stored around zero, streams are read evenly and mixed by the identity,
+        state-space heads decay at rates from 1/16 to 1 with steps around 0.1, time-mix channels
+        keep 0.95 of their state per token, blends take half of the previous token."""
+        import math
+
+        import torch
+        leaf = name.rsplit(".", 1)[-1]
+        if leaf in ("norm1", "norm2") or name in ("final.norm",) or leaf in ("b", "w0"):
+            return {"w0": -3.0}.get(leaf, 0.0)
+        if leaf == "in" and ".hc" in name:
+            return 1.0 / shape[0]
+        if leaf == "mix" and ".hc" in name:
+            return torch.eye(shape[0])
+        if leaf == "A_log":
+            return torch.linspace(math.log(1.0 / 16.0), 0.0, shape[0])
+        if leaf == "dt_bias":
+            return -2.25
+        if leaf == "conv":
+            taps = torch.full(shape, 0.1)
+            taps[:, -1] = 1.0
+            return taps
+        if leaf in ("r", "k", "v", "g", "w") and ".mu." in name:
+            return 0.5
+        if leaf in ("act", "u"):
+            return 0.5
+        return None
+
     def layer_runs(self) -> Tuple[int, ...]:
         """The layers in the order they run."""
         count = len(self.layers)

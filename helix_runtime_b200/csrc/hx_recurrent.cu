@@ -19,10 +19,19 @@
 // logarithms, the matrices and the sums over them are float32 throughout; projections arrive
 // in the compute type, as their products stored them.
 //
-// Both recurrences run one CTA per (request, head).  A thread owns a column of S (one value
-// coordinate) and a share of its rows: the rows are dealt to `parts` neighbouring lanes, which
-// add their partial sums with shuffles.  The tokens' vectors are staged through shared memory
-// a tile at a time, with the exponentials taken once per tile, not once per thread.
+// Both recurrences run CTAs per (request, head, block of columns).  A thread owns a column of S
+// (one value coordinate) and a run of consecutive rows of it (4, 8 or 16, by the matrix's size):
+// `parts` neighbouring lanes share a
+// column and add their partial sums with shuffles.  The tokens' vectors are staged through
+// shared memory a tile at a time (loads issued four at a time, the exponentials taken once
+// per token and channel, not once per thread), each lane's rows of a vector lying together
+// (padded against bank conflicts) so that 16-byte loads fetch them.  CTAs are
+// small (128 threads) so that several share an SM and one's staging hides behind another's
+// arithmetic.  In memory a head's matrix is laid out for exactly this dealing,
+// [row % run][column][row / run]: the k-th value of every thread is one contiguous run, so that
+// loading and storing the state (all a decode step does here) are full-width transactions.
+// Rows beyond the matrix (when the run does not divide them) are padding;
+// hx_scan_state_floats() gives the size.
 #include "hx_common.cuh"
 
 namespace {
@@ -105,7 +114,19 @@ __global__ __launch_bounds__(256) void causal_filter_kernel(const FilterArgs<T> 
 
 // ------------------------------------------------------------ state-space recurrence
 
-constexpr int ROWS_PER_THREAD = 16;
+// Rows of a column that one lane keeps.  A pure function of the row count, because the state's
+// order in memory follows from it.  Sixteen for every size: runs of 4 and 8 (more lanes and
+// CTAs per head, each staging the tokens' vectors again) were measured at the sizes of a 7B
+// model's layers and lost, 2.0 against 1.26 ms for 2,048 tokens of a state-space layer and
+// 190 against 68 us for a decode step of 64 requests of a time-mixing layer.
+__host__ __device__ constexpr int rows_per_thread(int rows) { return rows > 0 ? 16 : 16; }
+// Threads of a CTA at most.  A head whose columns need more is cut into blocks of columns
+// (blockIdx.z), each a CTA of its own with the same tokens staged.
+constexpr int SCAN_THREADS = 256;
+// CTAs the compiler makes room for on an SM (it bounds the registers of a thread).
+#ifndef HX_SCAN_CTAS
+#define HX_SCAN_CTAS 2
+#endif
 
 template <typename T>
 struct ScanArgs {
@@ -118,19 +139,54 @@ struct ScanArgs {
   const float* dt_bias;   // [heads]
   const float* a_log;     // [heads]
   const float* skip;      // [heads]
-  float* state;           // per slot: [heads, state, width]
+  float* state;           // per slot: heads x head_stride, see the layout above
   long long state_stride;
+  int head_stride;
   float* y;               // [tokens, heads * width]
   const int* request_start;
   const int* request_slot;
   int heads, width, rows, groups;   // rows = state size N
   int parts;                        // lanes that share a column
+  int block_lanes;                  // lanes (columns x parts) of one CTA
   int tile;                         // tokens staged at once
+  int per_token;                    // floats staged per token
 };
 
-template <typename T>
-__global__ void state_space_scan_kernel(const ScanArgs<T> a) {
-  extern __shared__ float shared[];
+// Rows of a staged vector are kept in runs of RPT (one lane's share); runs of eight and more
+// have four floats of padding behind them, so that the lanes of a warp, which read different
+// runs with 16-byte loads, fall on different banks.
+template <int RPT> constexpr int run_stride() { return RPT + (RPT >= 8 ? 4 : 0); }
+template <int RPT>
+__device__ __forceinline__ int padded(int n) { return n + (n / RPT) * (RPT >= 8 ? 4 : 0); }
+
+// One vector of `length` elements for each of `tokens` tokens: dst[t * stride + place(e)] =
+// load(t, e).  Warps take tokens, lanes take elements (consecutive addresses), four loads in
+// flight per lane; nothing divides.
+template <typename Load, typename Place>
+__device__ __forceinline__ void stage(float* dst, int stride, int tokens, int length, Load load,
+                                      Place place) {
+  const int warp = threadIdx.x >> 5;
+  const int warps = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int t = warp; t < tokens; t += warps) {
+    float* row = dst + t * stride;
+    for (int first = lane; first < length; first += 128) {
+      float v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (first + 32 * u < length) v[u] = load(t, first + 32 * u);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (first + 32 * u < length) row[place(first + 32 * u)] = v[u];
+    }
+  }
+}
+
+template <typename T, int ROWS_PER_THREAD>
+__global__ __launch_bounds__(SCAN_THREADS, HX_SCAN_CTAS) void state_space_scan_kernel(const ScanArgs<T> a) {
+  constexpr int STRIDE = run_stride<ROWS_PER_THREAD>();
+  extern __shared__ float4 shared4[];
+  float* shared = reinterpret_cast<float*>(shared4);
   hx_pdl_prologue();
   const int request = blockIdx.x;
   const int head = blockIdx.y;
@@ -138,70 +194,84 @@ __global__ void state_space_scan_kernel(const ScanArgs<T> a) {
   const int start = a.request_start[request];
   const int count = a.request_start[request + 1] - start;
   const int parts = a.parts;
-  const int column = threadIdx.x / parts;
-  const int part = threadIdx.x - column * parts;
-  const bool live = column < a.width;
-  // staged per token: B [rows], C [rows], x [width], step size, decay
-  const int per_token = 2 * a.rows + a.width + 2;
+  const int rows = a.rows;
+  const int width = a.width;
+  const int lane = blockIdx.z * a.block_lanes + threadIdx.x;    // among the head's lanes
+  const int column = lane / parts;
+  const int part = lane - column * parts;
+  const bool live = column < width && threadIdx.x < a.block_lanes;
+  // staged per token: B and C (parts runs each), x [width], step size, decay
+  const int run = parts * STRIDE;
+  const int per_token = a.per_token;
+  const int lanes = width * parts;       // threads of a head that own state
   float* s_state = a.state + static_cast<size_t>(a.request_slot[request]) * a.state_stride +
-                   static_cast<size_t>(head) * a.rows * a.width;
+                   static_cast<size_t>(head) * a.head_stride;
   float S[ROWS_PER_THREAD];
 #pragma unroll
   for (int k = 0; k < ROWS_PER_THREAD; ++k) {
-    const int n = part + k * parts;
-    S[k] = (live && n < a.rows) ? s_state[static_cast<size_t>(n) * a.width + column] : 0.0f;
+    const int n = part * ROWS_PER_THREAD + k;
+    S[k] = (live && n < rows) ? s_state[static_cast<size_t>(k) * lanes + lane] : 0.0f;
   }
+  // rows the matrix does not have stay zero in the staged vectors: nothing is guarded below
+  for (int i = threadIdx.x; i < a.tile * per_token; i += blockDim.x) shared[i] = 0.0f;
   const float rate = expf(a.a_log[head]);
   const float bias = a.dt_bias[head];
   const float skip = a.skip[head];
+  const size_t ld = a.ld;
   for (int base = 0; base < count; base += a.tile) {
     const int here = min(a.tile, count - base);
+    const size_t first = static_cast<size_t>(start + base);
     __syncthreads();
-    for (int i = threadIdx.x; i < here * per_token; i += blockDim.x) {
-      const int t = i / per_token;
-      const int e = i - t * per_token;
-      const size_t token = static_cast<size_t>(start + base + t);
-      float v;
-      if (e < a.rows) {
-        v = hx_to_float<T>(a.b[token * a.ld + group * a.rows + e]);
-      } else if (e < 2 * a.rows) {
-        v = hx_to_float<T>(a.c[token * a.ld + group * a.rows + (e - a.rows)]);
-      } else if (e < 2 * a.rows + a.width) {
-        v = hx_to_float<T>(a.x[token * a.ld + head * a.width + (e - 2 * a.rows)]);
-      } else {
-        const float step = softplus(hx_to_float<T>(a.dt[token * a.ld_dt + head]) + bias);
-        v = e == 2 * a.rows + a.width ? step : expf(-rate * step);
-      }
-      shared[i] = v;
+    const T* b = a.b + first * ld + group * rows;
+    const T* c = a.c + first * ld + group * rows;
+    const T* x = a.x + first * ld + head * width;
+    stage(shared, per_token, here, rows,
+          [&](int t, int e) { return hx_to_float<T>(b[t * ld + e]); }, padded<ROWS_PER_THREAD>);
+    stage(shared + run, per_token, here, rows,
+          [&](int t, int e) { return hx_to_float<T>(c[t * ld + e]); }, padded<ROWS_PER_THREAD>);
+    stage(shared + 2 * run, per_token, here, width,
+          [&](int t, int e) { return hx_to_float<T>(x[t * ld + e]); }, [](int e) { return e; });
+    for (int t = threadIdx.x; t < here; t += blockDim.x) {
+      const float step = softplus(hx_to_float<T>(a.dt[(first + t) * a.ld_dt + head]) + bias);
+      shared[t * per_token + 2 * run + width] = step;
+      shared[t * per_token + 2 * run + width + 1] = expf(-rate * step);
     }
     __syncthreads();
+    float* y_out = a.y + first * (a.heads * width) + head * width + column;
+#pragma unroll 1
     for (int t = 0; t < here; ++t) {
       const float* row = shared + t * per_token;
-      const float step = row[2 * a.rows + a.width];
-      const float decay = row[2 * a.rows + a.width + 1];
-      const float xv = live ? row[2 * a.rows + column] : 0.0f;
+      const float4* b4 = reinterpret_cast<const float4*>(row + part * STRIDE);
+      const float4* c4 = reinterpret_cast<const float4*>(row + run + part * STRIDE);
+      const float step = row[2 * run + width];
+      const float decay = row[2 * run + width + 1];
+      const float xv = live ? row[2 * run + column] : 0.0f;
       const float push = step * xv;
-      float sum = 0.0f;
+      float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
-      for (int k = 0; k < ROWS_PER_THREAD; ++k) {
-        const int n = part + k * parts;
-        if (n < a.rows) {
-          S[k] = fmaf(decay, S[k], row[n] * push);
-          sum = fmaf(S[k], row[a.rows + n], sum);
-        }
+      for (int q = 0; q < ROWS_PER_THREAD / 4; ++q) {
+        const float4 bv = b4[q];
+        const float4 cv = c4[q];
+        S[4 * q + 0] = fmaf(decay, S[4 * q + 0], bv.x * push);
+        S[4 * q + 1] = fmaf(decay, S[4 * q + 1], bv.y * push);
+        S[4 * q + 2] = fmaf(decay, S[4 * q + 2], bv.z * push);
+        S[4 * q + 3] = fmaf(decay, S[4 * q + 3], bv.w * push);
+        sum0 = fmaf(S[4 * q + 0], cv.x, sum0);
+        sum1 = fmaf(S[4 * q + 1], cv.y, sum1);
+        sum0 = fmaf(S[4 * q + 2], cv.z, sum0);
+        sum1 = fmaf(S[4 * q + 3], cv.w, sum1);
       }
+      float sum = sum0 + sum1;
       for (int offset = parts >> 1; offset > 0; offset >>= 1)
         sum += __shfl_xor_sync(0xffffffffu, sum, offset);
-      if (live && part == 0)
-        a.y[static_cast<size_t>(start + base + t) * (a.heads * a.width) + head * a.width + column] =
-            fmaf(skip, xv, sum);
+      if (live && part == 0) y_out[static_cast<size_t>(t) * (a.heads * width)] = fmaf(skip, xv, sum);
     }
   }
   if (live) {
 #pragma unroll
     for (int k = 0; k < ROWS_PER_THREAD; ++k) {
-      const int n = part + k * parts;
-      if (n < a.rows) s_state[static_cast<size_t>(n) * a.width + column] = S[k];
+      const int n = part * ROWS_PER_THREAD + k;
+      if (n < rows) s_state[static_cast<size_t>(k) * lanes + lane] = S[k];
     }
   }
 }
@@ -251,18 +321,21 @@ struct OuterScanArgs {
   int ld_decay;
   const float* w0;          // [heads * dim]
   const float* bonus;       // [heads, dim]
-  float* state;             // per slot: [heads, dim (key), dim (value)]
+  float* state;             // per slot: heads x head_stride, see the layout above
   long long state_stride;
+  int head_stride;
   float* o;                 // [tokens, heads * dim]
   const int* request_start;
   const int* request_slot;
   int heads, dim;
-  int parts, tile;
+  int parts, block_lanes, tile, per_token;
 };
 
-template <typename T>
-__global__ void outer_product_scan_kernel(const OuterScanArgs<T> a) {
-  extern __shared__ float shared[];
+template <typename T, int ROWS_PER_THREAD>
+__global__ __launch_bounds__(SCAN_THREADS, HX_SCAN_CTAS) void outer_product_scan_kernel(const OuterScanArgs<T> a) {
+  constexpr int STRIDE = run_stride<ROWS_PER_THREAD>();
+  extern __shared__ float4 shared4[];
+  float* shared = reinterpret_cast<float*>(shared4);
   hx_pdl_prologue();
   const int request = blockIdx.x;
   const int head = blockIdx.y;
@@ -270,68 +343,89 @@ __global__ void outer_product_scan_kernel(const OuterScanArgs<T> a) {
   const int count = a.request_start[request + 1] - start;
   const int parts = a.parts;
   const int dim = a.dim;
-  const int column = threadIdx.x / parts;
-  const int part = threadIdx.x - column * parts;
-  const bool live = column < dim;
-  const int per_token = 4 * dim;   // r, k, w, v
+  const int lane = blockIdx.z * a.block_lanes + threadIdx.x;
+  const int column = lane / parts;
+  const int part = lane - column * parts;
+  const bool live = column < dim && threadIdx.x < a.block_lanes;
+  // staged per token: r, k, w, bonus * k (parts runs each), v [dim]
+  const int run = parts * STRIDE;
+  const int per_token = a.per_token;
+  const int lanes = dim * parts;
   float* s_state = a.state + static_cast<size_t>(a.request_slot[request]) * a.state_stride +
-                   static_cast<size_t>(head) * dim * dim;
+                   static_cast<size_t>(head) * a.head_stride;
   float S[ROWS_PER_THREAD];
-  float u[ROWS_PER_THREAD];
 #pragma unroll
   for (int i = 0; i < ROWS_PER_THREAD; ++i) {
-    const int n = part + i * parts;
-    const bool have = live && n < dim;
-    S[i] = have ? s_state[static_cast<size_t>(n) * dim + column] : 0.0f;
-    u[i] = n < dim ? a.bonus[head * dim + n] : 0.0f;
+    const int n = part * ROWS_PER_THREAD + i;
+    S[i] = (live && n < dim) ? s_state[static_cast<size_t>(i) * lanes + lane] : 0.0f;
   }
+  for (int i = threadIdx.x; i < a.tile * per_token; i += blockDim.x) shared[i] = 0.0f;
+  const int channel0 = head * dim;
   for (int base = 0; base < count; base += a.tile) {
     const int here = min(a.tile, count - base);
+    const size_t first = static_cast<size_t>(start + base);
     __syncthreads();
-    for (int i = threadIdx.x; i < here * per_token; i += blockDim.x) {
-      const int t = i / per_token;
-      const int e = i - t * per_token;
-      const int which = e / dim;
-      const int d = e - which * dim;
-      const size_t token = static_cast<size_t>(start + base + t);
-      const int channel = head * dim + d;
-      float value;
-      if (which == 0) {
-        value = hx_to_float<T>(a.r[token * a.ld_r + channel]);
-      } else if (which == 1) {
-        value = hx_to_float<T>(a.k[token * a.ld_k + channel]);
-      } else if (which == 2) {
-        value = expf(-expf(a.decay_log[token * a.ld_decay + channel] + a.w0[channel]));
-      } else {
-        value = hx_to_float<T>(a.v[token * a.ld_v + channel]);
-      }
-      shared[i] = value;
-    }
+    const T* r = a.r + first * a.ld_r + channel0;
+    const T* k = a.k + first * a.ld_k + channel0;
+    const T* v = a.v + first * a.ld_v + channel0;
+    const float* decay_log = a.decay_log + first * a.ld_decay + channel0;
+    const float* w0 = a.w0 + channel0;
+    const float* bonus = a.bonus + channel0;
+    stage(shared, per_token, here, dim,
+          [&](int t, int e) { return hx_to_float<T>(r[static_cast<size_t>(t) * a.ld_r + e]); }, padded<ROWS_PER_THREAD>);
+    stage(shared + run, per_token, here, dim,
+          [&](int t, int e) { return hx_to_float<T>(k[static_cast<size_t>(t) * a.ld_k + e]); }, padded<ROWS_PER_THREAD>);
+    stage(shared + 2 * run, per_token, here, dim,
+          [&](int t, int e) {
+            return expf(-expf(decay_log[static_cast<size_t>(t) * a.ld_decay + e] + w0[e]));
+          },
+          padded<ROWS_PER_THREAD>);
+    stage(shared + 3 * run, per_token, here, dim,
+          [&](int t, int e) {
+            return bonus[e] * hx_to_float<T>(k[static_cast<size_t>(t) * a.ld_k + e]);
+          },
+          padded<ROWS_PER_THREAD>);
+    stage(shared + 4 * run, per_token, here, dim,
+          [&](int t, int e) { return hx_to_float<T>(v[static_cast<size_t>(t) * a.ld_v + e]); },
+          [](int e) { return e; });
     __syncthreads();
+    float* o_out = a.o + first * (a.heads * dim) + channel0 + column;
+#pragma unroll 1
     for (int t = 0; t < here; ++t) {
       const float* row = shared + t * per_token;
-      const float vj = live ? row[3 * dim + column] : 0.0f;
-      float sum = 0.0f;
+      const float4* r4 = reinterpret_cast<const float4*>(row + part * STRIDE);
+      const float4* k4 = reinterpret_cast<const float4*>(row + run + part * STRIDE);
+      const float4* w4 = reinterpret_cast<const float4*>(row + 2 * run + part * STRIDE);
+      const float4* u4 = reinterpret_cast<const float4*>(row + 3 * run + part * STRIDE);
+      const float vj = live ? row[4 * run + column] : 0.0f;
+      float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
-      for (int i = 0; i < ROWS_PER_THREAD; ++i) {
-        const int n = part + i * parts;
-        if (n < dim) {
-          const float pair = row[dim + n] * vj;
-          sum = fmaf(row[n], fmaf(u[i], pair, S[i]), sum);
-          S[i] = fmaf(row[2 * dim + n], S[i], pair);
-        }
+      for (int q = 0; q < ROWS_PER_THREAD / 4; ++q) {
+        const float4 rv = r4[q];
+        const float4 kv = k4[q];
+        const float4 wv = w4[q];
+        const float4 uv = u4[q];          // bonus * k
+        const float p0 = kv.x * vj, p1 = kv.y * vj, p2 = kv.z * vj, p3 = kv.w * vj;
+        sum0 = fmaf(rv.x, fmaf(uv.x, vj, S[4 * q + 0]), sum0);
+        sum1 = fmaf(rv.y, fmaf(uv.y, vj, S[4 * q + 1]), sum1);
+        sum0 = fmaf(rv.z, fmaf(uv.z, vj, S[4 * q + 2]), sum0);
+        sum1 = fmaf(rv.w, fmaf(uv.w, vj, S[4 * q + 3]), sum1);
+        S[4 * q + 0] = fmaf(wv.x, S[4 * q + 0], p0);
+        S[4 * q + 1] = fmaf(wv.y, S[4 * q + 1], p1);
+        S[4 * q + 2] = fmaf(wv.z, S[4 * q + 2], p2);
+        S[4 * q + 3] = fmaf(wv.w, S[4 * q + 3], p3);
       }
+      float sum = sum0 + sum1;
       for (int offset = parts >> 1; offset > 0; offset >>= 1)
         sum += __shfl_xor_sync(0xffffffffu, sum, offset);
-      if (live && part == 0)
-        a.o[static_cast<size_t>(start + base + t) * (a.heads * dim) + head * dim + column] = sum;
+      if (live && part == 0) o_out[static_cast<size_t>(t) * (a.heads * dim)] = sum;
     }
   }
   if (live) {
 #pragma unroll
     for (int i = 0; i < ROWS_PER_THREAD; ++i) {
-      const int n = part + i * parts;
-      if (n < dim) s_state[static_cast<size_t>(n) * dim + column] = S[i];
+      const int n = part * ROWS_PER_THREAD + i;
+      if (n < dim) s_state[static_cast<size_t>(i) * lanes + lane] = S[i];
     }
   }
 }
@@ -371,23 +465,38 @@ __global__ __launch_bounds__(128) void gated_group_norm_kernel(
   }
 }
 
-// lanes that share a column: the smallest power of two that leaves a thread at most
-// ROWS_PER_THREAD rows; 0 when even a whole warp would not do
+// lanes that share a column: the smallest power of two that leaves a lane at most
+// rows_per_thread(rows) rows; 0 when even a whole warp would not do
 int parts_for(int rows) {
   for (int parts = 1; parts <= 32; parts <<= 1)
-    if (parts * ROWS_PER_THREAD >= rows) return parts;
+    if (parts * rows_per_thread(rows) >= rows) return parts;
   return 0;
 }
 
-// tokens staged per tile so that the tile fits the shared memory a CTA gets without asking
+int state_floats(int columns, int rows) {
+  const int parts = parts_for(rows);
+  return parts * rows_per_thread(rows) * columns;
+}
+
+// floats staged per token: `vectors` vectors of `rows` rows in padded runs, and `plain` more;
+// a multiple of four, so that every token's runs start on 16 bytes
+int staged_floats(int vectors, int rows, int plain) {
+  const int rpt = rows_per_thread(rows);
+  return (vectors * parts_for(rows) * (rpt + (rpt >= 8 ? 4 : 0)) + plain + 3) / 4 * 4;
+}
+
+// tokens staged per tile: a tile of at most 24 KB, so that several CTAs share an SM
 int tile_for(int floats_per_token) {
-  const int budget = 40 * 1024 / 4;
+  const int budget = 24 * 1024 / 4;
   int tile = budget / floats_per_token;
   if (tile > 32) tile = 32;
   return tile;
 }
 
 }  // namespace
+
+// Floats a head's matrix of `rows` x `columns` takes in a request's state row.
+HX_API int hx_scan_state_floats(int columns, int rows) { return state_floats(columns, rows); }
 
 HX_API int hx_causal_filter(const void* raw, int ld_raw, void* out, int ld_out, int dtype,
                             const float* taps_weight, const float* bias, float* state,
@@ -418,38 +527,48 @@ HX_API int hx_causal_filter(const void* raw, int ld_raw, void* out, int ld_out, 
 
 HX_API int hx_state_space_scan(const void* x, const void* b, const void* c, int ld, const void* dt,
                                int ld_dt, int dtype, const float* dt_bias, const float* a_log,
-                               const float* skip, float* state, long long state_stride, float* y,
-                               const int* request_start, const int* request_slot, int requests,
+                               const float* skip, float* state, long long state_stride,
+                               int head_stride, float* y, const int* request_start, const int* request_slot, int requests,
                                int heads, int width, int rows, int groups, cudaStream_t stream) {
   HX_REQUIRE(requests >= 0 && heads > 0 && width > 0 && rows > 0 && groups > 0,
              "hx_state_space_scan: bad sizes");
   HX_REQUIRE(heads % groups == 0, "hx_state_space_scan: heads must be a multiple of groups");
   const int parts = parts_for(rows);
-  HX_REQUIRE(parts > 0, "hx_state_space_scan: a state of %d rows is more than %d", rows,
-             32 * ROWS_PER_THREAD);
-  const int threads = (width * parts + 31) / 32 * 32;
-  HX_REQUIRE(threads <= 1024, "hx_state_space_scan: heads of %d with a state of %d need %d threads",
-             width, rows, threads);
-  const int per_token = 2 * rows + width + 2;
+  HX_REQUIRE(parts > 0, "hx_state_space_scan: a state of %d rows is more than %d", rows, 32 * 16);
+  const int block_lanes = min(width, SCAN_THREADS / parts) * parts;
+  const int threads = (block_lanes + 31) / 32 * 32;
+  const int column_blocks = (width * parts + block_lanes - 1) / block_lanes;
+  HX_REQUIRE(head_stride >= state_floats(width, rows),
+             "hx_state_space_scan: a head's state takes %d floats, not %d", state_floats(width, rows),
+             head_stride);
+  const int per_token = staged_floats(2, rows, width + 2);
   const int tile = tile_for(per_token);
   HX_REQUIRE(tile >= 1, "hx_state_space_scan: a token's vectors do not fit shared memory");
   if (requests == 0) return HX_OK;
-  const dim3 grid(requests, heads);
+  const dim3 grid(requests, heads, column_blocks);
   const size_t shared_bytes = static_cast<size_t>(tile) * per_token * sizeof(float);
   if (dtype == HX_F32) {
     ScanArgs<float> a{static_cast<const float*>(x), static_cast<const float*>(b),
                       static_cast<const float*>(c), ld, static_cast<const float*>(dt), ld_dt,
-                      dt_bias, a_log, skip, state, state_stride, y, request_start, request_slot,
-                      heads, width, rows, groups, parts, tile};
-    hx_launch(state_space_scan_kernel<float>, grid, threads, shared_bytes, stream, a);
+                      dt_bias, a_log, skip, state, state_stride, head_stride, y, request_start,
+                      request_slot, heads, width, rows, groups, parts, block_lanes, tile, per_token};
+    switch (rows_per_thread(rows)) {
+      case 4: hx_launch(state_space_scan_kernel<float, 4>, grid, threads, shared_bytes, stream, a); break;
+      case 8: hx_launch(state_space_scan_kernel<float, 8>, grid, threads, shared_bytes, stream, a); break;
+      default: hx_launch(state_space_scan_kernel<float, 16>, grid, threads, shared_bytes, stream, a);
+    }
   } else if (dtype == HX_BF16) {
     ScanArgs<__nv_bfloat16> a{static_cast<const __nv_bfloat16*>(x),
                               static_cast<const __nv_bfloat16*>(b),
                               static_cast<const __nv_bfloat16*>(c), ld,
                               static_cast<const __nv_bfloat16*>(dt), ld_dt, dt_bias, a_log, skip,
-                              state, state_stride, y, request_start, request_slot, heads, width,
-                              rows, groups, parts, tile};
-    hx_launch(state_space_scan_kernel<__nv_bfloat16>, grid, threads, shared_bytes, stream, a);
+                              state, state_stride, head_stride, y, request_start, request_slot,
+                              heads, width, rows, groups, parts, block_lanes, tile, per_token};
+    switch (rows_per_thread(rows)) {
+      case 4: hx_launch(state_space_scan_kernel<__nv_bfloat16, 4>, grid, threads, shared_bytes, stream, a); break;
+      case 8: hx_launch(state_space_scan_kernel<__nv_bfloat16, 8>, grid, threads, shared_bytes, stream, a); break;
+      default: hx_launch(state_space_scan_kernel<__nv_bfloat16, 16>, grid, threads, shared_bytes, stream, a);
+    }
   } else {
     HX_REQUIRE(false, "hx_state_space_scan: unknown dtype %d", dtype);
   }
@@ -482,33 +601,47 @@ HX_API int hx_token_shift(const void* h, int ld, int dtype, const float* mu, int
 HX_API int hx_outer_product_scan(const void* r, int ld_r, const void* k, int ld_k, const void* v,
                                  int ld_v, int dtype, const float* decay_log, int ld_decay,
                                  const float* w0, const float* bonus, float* state,
-                                 long long state_stride, float* o, const int* request_start,
+                                 long long state_stride, int head_stride, float* o,
+                                 const int* request_start,
                                  const int* request_slot, int requests, int heads, int dim,
                                  cudaStream_t stream) {
   HX_REQUIRE(requests >= 0 && heads > 0 && dim > 0, "hx_outer_product_scan: bad sizes");
   const int parts = parts_for(dim);
-  HX_REQUIRE(parts > 0, "hx_outer_product_scan: heads of %d are more than %d", dim,
-             32 * ROWS_PER_THREAD);
-  const int threads = (dim * parts + 31) / 32 * 32;
-  HX_REQUIRE(threads <= 1024, "hx_outer_product_scan: heads of %d need %d threads", dim, threads);
-  const int tile = tile_for(4 * dim);
+  HX_REQUIRE(parts > 0, "hx_outer_product_scan: heads of %d are more than %d", dim, 32 * 16);
+  const int block_lanes = min(dim, SCAN_THREADS / parts) * parts;
+  const int threads = (block_lanes + 31) / 32 * 32;
+  const int column_blocks = (dim * parts + block_lanes - 1) / block_lanes;
+  HX_REQUIRE(head_stride >= state_floats(dim, dim),
+             "hx_outer_product_scan: a head's state takes %d floats, not %d", state_floats(dim, dim),
+             head_stride);
+  const int per_token = staged_floats(4, dim, dim);
+  const int tile = tile_for(per_token);
   HX_REQUIRE(tile >= 1, "hx_outer_product_scan: a token's vectors do not fit shared memory");
   if (requests == 0) return HX_OK;
-  const dim3 grid(requests, heads);
-  const size_t shared_bytes = static_cast<size_t>(tile) * 4 * dim * sizeof(float);
+  const dim3 grid(requests, heads, column_blocks);
+  const size_t shared_bytes = static_cast<size_t>(tile) * per_token * sizeof(float);
   if (dtype == HX_F32) {
     OuterScanArgs<float> a{static_cast<const float*>(r), static_cast<const float*>(k),
                            static_cast<const float*>(v), ld_r, ld_k, ld_v, decay_log, ld_decay, w0,
-                           bonus, state, state_stride, o, request_start, request_slot, heads, dim,
-                           parts, tile};
-    hx_launch(outer_product_scan_kernel<float>, grid, threads, shared_bytes, stream, a);
+                           bonus, state, state_stride, head_stride, o, request_start, request_slot,
+                           heads, dim, parts, block_lanes, tile, per_token};
+    switch (rows_per_thread(dim)) {
+      case 4: hx_launch(outer_product_scan_kernel<float, 4>, grid, threads, shared_bytes, stream, a); break;
+      case 8: hx_launch(outer_product_scan_kernel<float, 8>, grid, threads, shared_bytes, stream, a); break;
+      default: hx_launch(outer_product_scan_kernel<float, 16>, grid, threads, shared_bytes, stream, a);
+    }
   } else if (dtype == HX_BF16) {
     OuterScanArgs<__nv_bfloat16> a{static_cast<const __nv_bfloat16*>(r),
                                    static_cast<const __nv_bfloat16*>(k),
                                    static_cast<const __nv_bfloat16*>(v), ld_r, ld_k, ld_v,
-                                   decay_log, ld_decay, w0, bonus, state, state_stride, o,
-                                   request_start, request_slot, heads, dim, parts, tile};
-    hx_launch(outer_product_scan_kernel<__nv_bfloat16>, grid, threads, shared_bytes, stream, a);
+                                   decay_log, ld_decay, w0, bonus, state, state_stride,
+                                   head_stride, o, request_start, request_slot, heads, dim, parts,
+                                   block_lanes, tile, per_token};
+    switch (rows_per_thread(dim)) {
+      case 4: hx_launch(outer_product_scan_kernel<__nv_bfloat16, 4>, grid, threads, shared_bytes, stream, a); break;
+      case 8: hx_launch(outer_product_scan_kernel<__nv_bfloat16, 8>, grid, threads, shared_bytes, stream, a); break;
+      default: hx_launch(outer_product_scan_kernel<__nv_bfloat16, 16>, grid, threads, shared_bytes, stream, a);
+    }
   } else {
     HX_REQUIRE(false, "hx_outer_product_scan: unknown dtype %d", dtype);
   }

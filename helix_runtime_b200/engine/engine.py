@@ -79,7 +79,10 @@ def random_model(config, seed: int, dtype: Union[str, torch.dtype] = "bfloat16",
                  device: Union[str, torch.device] = "cuda:0", std: float = 0.02) -> DecoderModel:
     """A model with seeded random weights made directly on the device (no folder): every
     matrix N(0, std), norm weights one.  Used where writing gigabytes to disk would only
-    cost time; :func:`write_random_model` is the mode that writes a folder."""
+    cost time; :func:`write_random_model` is the mode that writes a folder.  A configuration
+    whose per-channel vectors and small tables must not all be one (decay rates, weights stored
+    around zero, matrices that mix residual streams) says what they are filled with:
+    ``config.random_scale(name, shape)`` returns a number, a tensor, or None for ones."""
     dtype = parse_dtype(dtype)
     device = torch.device(device)
     architecture = architecture_for(config.to_dict())
@@ -90,7 +93,14 @@ def random_model(config, seed: int, dtype: Union[str, torch.dtype] = "bfloat16",
     tensors: Dict[str, torch.Tensor] = {}
     for request in model.tensor_requests():
         if request.role == "scale":
-            tensors[request.name] = torch.ones(request.shape, dtype=torch.float32, device=device)
+            fill = getattr(config, "random_scale", lambda name, shape: None)(request.name,
+                                                                             request.shape)
+            if isinstance(fill, torch.Tensor):
+                tensors[request.name] = fill.to(device=device, dtype=torch.float32) \
+                    .reshape(request.shape).contiguous()
+            else:
+                tensors[request.name] = torch.full(request.shape, 1.0 if fill is None else
+                                                   float(fill), dtype=torch.float32, device=device)
         else:
             value = torch.empty(request.shape, dtype=dtype, device=device)
             value.normal_(0.0, std, generator=generator)

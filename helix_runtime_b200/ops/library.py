@@ -139,8 +139,10 @@ def _declare(library: ctypes.CDLL) -> None:
     library.hx_causal_filter.argtypes = [_c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr,
                                          _c_ptr, _c_longlong, _c_int, _c_int, _c_int, _c_int, _c_ptr,
                                          _c_ptr, _c_ptr, _c_ptr]
+    library.hx_scan_state_floats.argtypes = [_c_int, _c_int]
+    library.hx_scan_state_floats.restype = _c_int
     library.hx_state_space_scan.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int,
-                                            _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_longlong, _c_ptr,
+                                            _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_longlong, _c_int, _c_ptr,
                                             _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
                                             _c_ptr]
     library.hx_token_shift.argtypes = [_c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_longlong,
@@ -148,7 +150,8 @@ def _declare(library: ctypes.CDLL) -> None:
                                        _c_ptr]
     library.hx_outer_product_scan.argtypes = [_c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int,
                                               _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_longlong,
-                                              _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr]
+                                              _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
+                                              _c_ptr]
     library.hx_gated_group_norm.argtypes = [_c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr,
                                             _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr]
     library.hx_norm_rotary_append.argtypes = [
@@ -675,6 +678,26 @@ def biased_activation(sums: torch.Tensor, bias: Optional[torch.Tensor], out: tor
 
 # ------------------------------------------------------------------------ recurrent mixers
 
+def scan_rows_per_thread(rows: int) -> int:
+    """Consecutive rows of a column that one lane of a recurrence keeps (the kernels' constant)."""
+    return 16
+
+
+def scan_state_floats(columns: int, rows: int) -> int:
+    """Floats that a head's ``rows x columns`` matrix takes in a request's state row.  The
+    recurrences give a run of consecutive rows of a column to a lane, ``parts`` lanes (a power of
+    two) to a column, and keep the matrix in that order, padded to whole runs.  Computed here so
+    that a model can be sized without a GPU; the kernels refuse a state that is smaller than
+    their own count."""
+    run = scan_rows_per_thread(rows)
+    parts = 1
+    while parts * run < rows:
+        parts *= 2
+    if parts > 32:
+        raise KernelError(f"a recurrence over {rows} rows is more than 512")
+    return parts * run * columns
+
+
 def causal_filter(raw: torch.Tensor, out: torch.Tensor, taps: torch.Tensor,
                   bias: Optional[torch.Tensor], state: Optional[torch.Tensor], tokens: int,
                   silu: bool, token_request: torch.Tensor, request_slot: torch.Tensor,
@@ -715,11 +738,12 @@ def state_space_scan(x: torch.Tensor, b: torch.Tensor, c: torch.Tensor, dt: torc
     assert x.dtype == b.dtype == c.dtype == dt.dtype
     assert x.stride(0) == b.stride(0) == c.stride(0) and x.stride(-1) == 1 and dt.stride(-1) == 1
     assert y.is_contiguous() and y.shape[1] == heads * width
-    assert state.shape[1] >= heads * rows * width
+    head_stride = scan_state_floats(width, rows)
+    assert state.shape[1] >= heads * head_stride
     _check(lib().hx_state_space_scan(x.data_ptr(), b.data_ptr(), c.data_ptr(), x.stride(0),
                                      dt.data_ptr(), dt.stride(0), dtype_code(x.dtype),
                                      dt_bias.data_ptr(), a_log.data_ptr(), skip.data_ptr(),
-                                     state.data_ptr(), state.stride(0), y.data_ptr(),
+                                     state.data_ptr(), state.stride(0), head_stride, y.data_ptr(),
                                      request_start.data_ptr(), request_slot.data_ptr(), requests,
                                      heads, width, rows, groups, _stream()))
 
@@ -747,17 +771,19 @@ def outer_product_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_
                        heads: int, dim: int) -> None:
     """Per head ``o = (S + diag(bonus) k v')' r`` then ``S = diag(w) S + k v'`` with
     ``w = exp(-exp(decay_log + w0))``; ``r``, ``k``, ``v`` ``[tokens, heads * dim]`` in the compute
-    dtype, ``decay_log`` and ``o`` float32, ``state`` ``[slots, >= heads * dim * dim]`` float32."""
+    dtype, ``decay_log`` and ``o`` float32, ``state`` ``[slots, >= heads * scan_state_floats(dim,
+    dim)]`` float32."""
     for name, tensor in (("decay_log", decay_log), ("w0", w0), ("bonus", bonus), ("state", state),
                          ("o", o)):
         _need(tensor, torch.float32, name)
     assert r.dtype == k.dtype == v.dtype and o.is_contiguous() and o.shape[1] == heads * dim
-    assert state.shape[1] >= heads * dim * dim
+    head_stride = scan_state_floats(dim, dim)
+    assert state.shape[1] >= heads * head_stride
     _check(lib().hx_outer_product_scan(r.data_ptr(), r.stride(0), k.data_ptr(), k.stride(0),
                                        v.data_ptr(), v.stride(0), dtype_code(r.dtype),
                                        decay_log.data_ptr(), decay_log.stride(0), w0.data_ptr(),
                                        bonus.data_ptr(), state.data_ptr(), state.stride(0),
-                                       o.data_ptr(), request_start.data_ptr(),
+                                       head_stride, o.data_ptr(), request_start.data_ptr(),
                                        request_slot.data_ptr(), requests, heads, dim, _stream()))
 
 

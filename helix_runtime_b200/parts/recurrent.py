@@ -13,15 +13,16 @@ dt: heads]``; ``x, B, C`` pass a causal per-channel filter with bias, then silu;
 ``d = softplus(dt + dt_bias)``; per head (head ``h`` reads group ``h // (heads / G)``)
 ``S_t = exp(-exp(A_log) d_t) S_(t-1) + d_t B_t x_t'``, ``y_t = S_t' C_t + D x_t``; ``y silu(z)``
 is RMS-normed in ``norm_groups`` equal parts, times ``norm``, then the output projection.
-State: the filter's last ``filter_taps - 1`` inputs and ``S`` ``[heads, N, P]``.
+State: the filter's last ``filter_taps - 1`` inputs and the matrices ``S`` (in the scan
+kernel's own order, ``ops.scan_state_floats`` floats per head).
 
 :class:`TimeMix` (``time_mix``).  Parameters ``heads``, ``head_dim``, ``decay_rank``, ``eps``.
 With ``h'`` the previous token's input, each of r, k, v, g, w reads ``h + (h' - h) mu_s``;
 ``r, k, v`` are projections of their blends, ``gate = silu(W_g m_g)``,
 ``w = exp(-exp(W_w2 tanh(W_w1 m_w) + w0))``; per head ``o_t = (S_(t-1) + diag(u) k_t v_t')' r_t``
 then ``S_t = diag(w_t) S_(t-1) + k_t v_t'``; each head's ``o`` over its root mean square, times
-``norm``, times the gate, then the output projection.  State: ``h'`` and ``S``
-``[heads, head_dim, head_dim]``.
+``norm``, times the gate, then the output projection.  State: ``h'`` and the
+matrices ``S`` (``ops.scan_state_floats`` floats per head).
 
 :class:`SideBySide` (``side_by_side``).  Parameters ``mixers`` (part specs) and ``scales``: every
 mixer reads the same input and the result is ``sum_i scales[i] * mixer_i(x)``, summed in float32.
@@ -67,7 +68,7 @@ class StateSpaceMixer(Mixer):
         self.filtered = self.inner + 2 * self.groups * self.state_size
         self.projected = 2 * self.inner + 2 * self.groups * self.state_size + self.heads
         self.filter_state = (self.taps - 1) * self.filtered
-        self.matrix_state = self.heads * self.state_size * self.head_width
+        self.matrix_state = self.heads * ops.scan_state_floats(self.head_width, self.state_size)
         self.names = dict(spec.tensors)
         self.w_in: Optional[Weight] = None
         self.w_o: Optional[Weight] = None
@@ -139,7 +140,7 @@ class TimeMix(Mixer):
         self.decay_rank = int(spec["decay_rank"])
         self.eps = float(spec["eps"])
         self.width = self.heads * self.head_dim
-        self.matrix_state = self.heads * self.head_dim * self.head_dim
+        self.matrix_state = self.heads * ops.scan_state_floats(self.head_dim, self.head_dim)
         self.names = dict(spec.tensors)
         self.weights: dict = {}
 

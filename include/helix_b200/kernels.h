@@ -140,13 +140,15 @@ int hx_causal_filter(const void* raw, int ld_raw, void* out, int ld_out, int dty
                      long long state_stride, int taps, int channels, int silu, int tokens,
                      const int* token_request, const int* request_slot, const int* request_start,
                      cudaStream_t stream);
+/* floats that a head's rows x columns matrix takes in a state row (the kernels' own order) */
+int hx_scan_state_floats(int columns, int rows);
 /* per head: S = exp(-exp(a_log) d) S + d B x', y = S' C + skip x, d = softplus(dt + dt_bias);
- * state [heads][rows][width]; y float32 [tokens][heads * width] */
+ * state: heads x head_stride floats; y float32 [tokens][heads * width] */
 int hx_state_space_scan(const void* x, const void* b, const void* c, int ld, const void* dt,
                         int ld_dt, int dtype, const float* dt_bias, const float* a_log,
-                        const float* skip, float* state, long long state_stride, float* y,
-                        const int* request_start, const int* request_slot, int requests, int heads,
-                        int width, int rows, int groups, cudaStream_t stream);
+                        const float* skip, float* state, long long state_stride, int head_stride,
+                        float* y, const int* request_start, const int* request_slot, int requests,
+                        int heads, int width, int rows, int groups, cudaStream_t stream);
 /* out[s][t] = h[t] + (h[t-1] - h[t]) * mu[s]; the state row [hidden] is the previous step's
  * last row and becomes this step's */
 int hx_token_shift(const void* h, int ld, int dtype, const float* mu, int mixes, void* out,
@@ -154,11 +156,12 @@ int hx_token_shift(const void* h, int ld, int dtype, const float* mu, int mixes,
                    int hidden, const int* token_request, const int* request_slot,
                    const int* request_start, cudaStream_t stream);
 /* per head: o = (S + diag(bonus) k v')' r, then S = diag(w) S + k v', w = exp(-exp(decay_log +
- * w0)); state [heads][dim][dim]; o float32 */
+ * w0)); state: heads x head_stride floats; o float32 */
 int hx_outer_product_scan(const void* r, int ld_r, const void* k, int ld_k, const void* v,
                           int ld_v, int dtype, const float* decay_log, int ld_decay,
                           const float* w0, const float* bonus, float* state,
-                          long long state_stride, float* o, const int* request_start,
+                          long long state_stride, int head_stride, float* o,
+                          const int* request_start,
                           const int* request_slot, int requests, int heads, int dim,
                           cudaStream_t stream);
 /* channels in `groups` equal parts, each over its root mean square, times weight; the gate

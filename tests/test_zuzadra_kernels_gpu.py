@@ -193,7 +193,8 @@ def test_state_space_scan(heads, width, rows, groups, dtype):
             rows_in[:, :inner].reshape(n, heads, width), rows_in[:, inner:inner + bc].reshape(n, groups, rows),
             rows_in[:, inner + bc:].reshape(n, groups, rows), plain.softplus(dt + dt_bias), a_log, skip,
             groups).reshape(n, inner))
-    state = torch.zeros((3, heads * rows * width + 3), dtype=torch.float32, device="cuda")
+    state = torch.zeros((3, heads * ops.scan_state_floats(width, rows) + 3), dtype=torch.float32,
+                        device="cuda")
     state[1] = float("nan")                       # a slot nobody owns is never read
     slots = [2, 0]
     got = [np.zeros_like(w) for w in want]
@@ -236,7 +237,8 @@ def test_outer_product_scan(heads, dim, dtype):
         want.append(plain.decayed_outer_product_scan(
             r.reshape(n, heads, dim), k.reshape(n, heads, dim), v.reshape(n, heads, dim),
             w.reshape(n, heads, dim), bonus).reshape(n, a))
-    state = torch.zeros((2, heads * dim * dim), dtype=torch.float32, device="cuda")
+    state = torch.zeros((2, heads * ops.scan_state_floats(dim, dim)), dtype=torch.float32,
+                        device="cuda")
     slots = [1, 0]
     got = [np.zeros_like(w) for w in want]
 
