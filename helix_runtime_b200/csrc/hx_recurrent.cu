@@ -162,9 +162,13 @@ __device__ __forceinline__ int padded(int n) { return n + (n / RPT) * (RPT >= 8 
 // One vector of `length` elements for each of `tokens` tokens: dst[t * stride + place(e)] =
 // load(t, e).  Warps take tokens, lanes take elements (consecutive addresses), four loads in
 // flight per lane; nothing divides.
-template <typename Load, typename Place>
+template <bool ONE_TOKEN, typename Load, typename Place>
 __device__ __forceinline__ void stage(float* dst, int stride, int tokens, int length, Load load,
                                       Place place) {
+  if (ONE_TOKEN) {      // a decode step: one vector, one load per thread and round
+    for (int e = threadIdx.x; e < length; e += blockDim.x) dst[place(e)] = load(0, e);
+    return;
+  }
   const int warp = threadIdx.x >> 5;
   const int warps = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -182,8 +186,12 @@ __device__ __forceinline__ void stage(float* dst, int stride, int tokens, int le
   }
 }
 
-template <typename T, int ROWS_PER_THREAD>
-__global__ __launch_bounds__(SCAN_THREADS, HX_SCAN_CTAS) void state_space_scan_kernel(const ScanArgs<T> a) {
+// ONE_TOKEN: every request of the step brings exactly one token (a decode step).  The kernel
+// then only loads a matrix, touches it once and stores it: its time is the state's bytes over
+// what the SM keeps in flight, so the compiler is held to fewer registers (three CTAs an SM).
+template <typename T, int ROWS_PER_THREAD, bool ONE_TOKEN>
+__global__ __launch_bounds__(SCAN_THREADS, ONE_TOKEN ? 3 : HX_SCAN_CTAS)
+void state_space_scan_kernel(const ScanArgs<T> a) {
   constexpr int STRIDE = run_stride<ROWS_PER_THREAD>();
   extern __shared__ float4 shared4[];
   float* shared = reinterpret_cast<float*>(shared4);
@@ -192,7 +200,7 @@ __global__ __launch_bounds__(SCAN_THREADS, HX_SCAN_CTAS) void state_space_scan_k
   const int head = blockIdx.y;
   const int group = head / (a.heads / a.groups);
   const int start = a.request_start[request];
-  const int count = a.request_start[request + 1] - start;
+  const int count = ONE_TOKEN ? 1 : a.request_start[request + 1] - start;
   const int parts = a.parts;
   const int rows = a.rows;
   const int width = a.width;
@@ -213,7 +221,8 @@ __global__ __launch_bounds__(SCAN_THREADS, HX_SCAN_CTAS) void state_space_scan_k
     S[k] = (live && n < rows) ? s_state[static_cast<size_t>(k) * lanes + lane] : 0.0f;
   }
   // rows the matrix does not have stay zero in the staged vectors: nothing is guarded below
-  for (int i = threadIdx.x; i < a.tile * per_token; i += blockDim.x) shared[i] = 0.0f;
+  for (int i = threadIdx.x; i < (ONE_TOKEN ? 1 : a.tile) * per_token; i += blockDim.x)
+    shared[i] = 0.0f;
   const float rate = expf(a.a_log[head]);
   const float bias = a.dt_bias[head];
   const float skip = a.skip[head];
@@ -225,11 +234,11 @@ __global__ __launch_bounds__(SCAN_THREADS, HX_SCAN_CTAS) void state_space_scan_k
     const T* b = a.b + first * ld + group * rows;
     const T* c = a.c + first * ld + group * rows;
     const T* x = a.x + first * ld + head * width;
-    stage(shared, per_token, here, rows,
+    stage<ONE_TOKEN>(shared, per_token, here, rows,
           [&](int t, int e) { return hx_to_float<T>(b[t * ld + e]); }, padded<ROWS_PER_THREAD>);
-    stage(shared + run, per_token, here, rows,
+    stage<ONE_TOKEN>(shared + run, per_token, here, rows,
           [&](int t, int e) { return hx_to_float<T>(c[t * ld + e]); }, padded<ROWS_PER_THREAD>);
-    stage(shared + 2 * run, per_token, here, width,
+    stage<ONE_TOKEN>(shared + 2 * run, per_token, here, width,
           [&](int t, int e) { return hx_to_float<T>(x[t * ld + e]); }, [](int e) { return e; });
     for (int t = threadIdx.x; t < here; t += blockDim.x) {
       const float step = softplus(hx_to_float<T>(a.dt[(first + t) * a.ld_dt + head]) + bias);
@@ -331,8 +340,9 @@ struct OuterScanArgs {
   int parts, block_lanes, tile, per_token;
 };
 
-template <typename T, int ROWS_PER_THREAD>
-__global__ __launch_bounds__(SCAN_THREADS, HX_SCAN_CTAS) void outer_product_scan_kernel(const OuterScanArgs<T> a) {
+template <typename T, int ROWS_PER_THREAD, bool ONE_TOKEN>
+__global__ __launch_bounds__(SCAN_THREADS, ONE_TOKEN ? 3 : HX_SCAN_CTAS)
+void outer_product_scan_kernel(const OuterScanArgs<T> a) {
   constexpr int STRIDE = run_stride<ROWS_PER_THREAD>();
   extern __shared__ float4 shared4[];
   float* shared = reinterpret_cast<float*>(shared4);
@@ -340,7 +350,7 @@ __global__ __launch_bounds__(SCAN_THREADS, HX_SCAN_CTAS) void outer_product_scan
   const int request = blockIdx.x;
   const int head = blockIdx.y;
   const int start = a.request_start[request];
-  const int count = a.request_start[request + 1] - start;
+  const int count = ONE_TOKEN ? 1 : a.request_start[request + 1] - start;
   const int parts = a.parts;
   const int dim = a.dim;
   const int lane = blockIdx.z * a.block_lanes + threadIdx.x;
@@ -359,7 +369,8 @@ __global__ __launch_bounds__(SCAN_THREADS, HX_SCAN_CTAS) void outer_product_scan
     const int n = part * ROWS_PER_THREAD + i;
     S[i] = (live && n < dim) ? s_state[static_cast<size_t>(i) * lanes + lane] : 0.0f;
   }
-  for (int i = threadIdx.x; i < a.tile * per_token; i += blockDim.x) shared[i] = 0.0f;
+  for (int i = threadIdx.x; i < (ONE_TOKEN ? 1 : a.tile) * per_token; i += blockDim.x)
+    shared[i] = 0.0f;
   const int channel0 = head * dim;
   for (int base = 0; base < count; base += a.tile) {
     const int here = min(a.tile, count - base);
@@ -371,21 +382,21 @@ __global__ __launch_bounds__(SCAN_THREADS, HX_SCAN_CTAS) void outer_product_scan
     const float* decay_log = a.decay_log + first * a.ld_decay + channel0;
     const float* w0 = a.w0 + channel0;
     const float* bonus = a.bonus + channel0;
-    stage(shared, per_token, here, dim,
+    stage<ONE_TOKEN>(shared, per_token, here, dim,
           [&](int t, int e) { return hx_to_float<T>(r[static_cast<size_t>(t) * a.ld_r + e]); }, padded<ROWS_PER_THREAD>);
-    stage(shared + run, per_token, here, dim,
+    stage<ONE_TOKEN>(shared + run, per_token, here, dim,
           [&](int t, int e) { return hx_to_float<T>(k[static_cast<size_t>(t) * a.ld_k + e]); }, padded<ROWS_PER_THREAD>);
-    stage(shared + 2 * run, per_token, here, dim,
+    stage<ONE_TOKEN>(shared + 2 * run, per_token, here, dim,
           [&](int t, int e) {
             return expf(-expf(decay_log[static_cast<size_t>(t) * a.ld_decay + e] + w0[e]));
           },
           padded<ROWS_PER_THREAD>);
-    stage(shared + 3 * run, per_token, here, dim,
+    stage<ONE_TOKEN>(shared + 3 * run, per_token, here, dim,
           [&](int t, int e) {
             return bonus[e] * hx_to_float<T>(k[static_cast<size_t>(t) * a.ld_k + e]);
           },
           padded<ROWS_PER_THREAD>);
-    stage(shared + 4 * run, per_token, here, dim,
+    stage<ONE_TOKEN>(shared + 4 * run, per_token, here, dim,
           [&](int t, int e) { return hx_to_float<T>(v[static_cast<size_t>(t) * a.ld_v + e]); },
           [](int e) { return e; });
     __syncthreads();
@@ -528,8 +539,9 @@ HX_API int hx_causal_filter(const void* raw, int ld_raw, void* out, int ld_out, 
 HX_API int hx_state_space_scan(const void* x, const void* b, const void* c, int ld, const void* dt,
                                int ld_dt, int dtype, const float* dt_bias, const float* a_log,
                                const float* skip, float* state, long long state_stride,
-                               int head_stride, float* y, const int* request_start, const int* request_slot, int requests,
-                               int heads, int width, int rows, int groups, cudaStream_t stream) {
+                               int head_stride, float* y, const int* request_start,
+                               const int* request_slot, int requests, int tokens, int heads,
+                               int width, int rows, int groups, cudaStream_t stream) {
   HX_REQUIRE(requests >= 0 && heads > 0 && width > 0 && rows > 0 && groups > 0,
              "hx_state_space_scan: bad sizes");
   HX_REQUIRE(heads % groups == 0, "hx_state_space_scan: heads must be a multiple of groups");
@@ -547,15 +559,25 @@ HX_API int hx_state_space_scan(const void* x, const void* b, const void* c, int 
   if (requests == 0) return HX_OK;
   const dim3 grid(requests, heads, column_blocks);
   const size_t shared_bytes = static_cast<size_t>(tile) * per_token * sizeof(float);
+  const bool one_token = tokens == requests;      // every request brings at least one
+  const size_t one_bytes = static_cast<size_t>(per_token) * sizeof(float);
   if (dtype == HX_F32) {
     ScanArgs<float> a{static_cast<const float*>(x), static_cast<const float*>(b),
                       static_cast<const float*>(c), ld, static_cast<const float*>(dt), ld_dt,
                       dt_bias, a_log, skip, state, state_stride, head_stride, y, request_start,
                       request_slot, heads, width, rows, groups, parts, block_lanes, tile, per_token};
-    switch (rows_per_thread(rows)) {
-      case 4: hx_launch(state_space_scan_kernel<float, 4>, grid, threads, shared_bytes, stream, a); break;
-      case 8: hx_launch(state_space_scan_kernel<float, 8>, grid, threads, shared_bytes, stream, a); break;
-      default: hx_launch(state_space_scan_kernel<float, 16>, grid, threads, shared_bytes, stream, a);
+    if (one_token) {
+      switch (rows_per_thread(rows)) {
+        case 4: hx_launch(state_space_scan_kernel<float, 4, true>, grid, threads, one_bytes, stream, a); break;
+        case 8: hx_launch(state_space_scan_kernel<float, 8, true>, grid, threads, one_bytes, stream, a); break;
+        default: hx_launch(state_space_scan_kernel<float, 16, true>, grid, threads, one_bytes, stream, a);
+      }
+    } else {
+      switch (rows_per_thread(rows)) {
+        case 4: hx_launch(state_space_scan_kernel<float, 4, false>, grid, threads, shared_bytes, stream, a); break;
+        case 8: hx_launch(state_space_scan_kernel<float, 8, false>, grid, threads, shared_bytes, stream, a); break;
+        default: hx_launch(state_space_scan_kernel<float, 16, false>, grid, threads, shared_bytes, stream, a);
+      }
     }
   } else if (dtype == HX_BF16) {
     ScanArgs<__nv_bfloat16> a{static_cast<const __nv_bfloat16*>(x),
@@ -564,10 +586,18 @@ HX_API int hx_state_space_scan(const void* x, const void* b, const void* c, int 
                               static_cast<const __nv_bfloat16*>(dt), ld_dt, dt_bias, a_log, skip,
                               state, state_stride, head_stride, y, request_start, request_slot,
                               heads, width, rows, groups, parts, block_lanes, tile, per_token};
-    switch (rows_per_thread(rows)) {
-      case 4: hx_launch(state_space_scan_kernel<__nv_bfloat16, 4>, grid, threads, shared_bytes, stream, a); break;
-      case 8: hx_launch(state_space_scan_kernel<__nv_bfloat16, 8>, grid, threads, shared_bytes, stream, a); break;
-      default: hx_launch(state_space_scan_kernel<__nv_bfloat16, 16>, grid, threads, shared_bytes, stream, a);
+    if (one_token) {
+      switch (rows_per_thread(rows)) {
+        case 4: hx_launch(state_space_scan_kernel<__nv_bfloat16, 4, true>, grid, threads, one_bytes, stream, a); break;
+        case 8: hx_launch(state_space_scan_kernel<__nv_bfloat16, 8, true>, grid, threads, one_bytes, stream, a); break;
+        default: hx_launch(state_space_scan_kernel<__nv_bfloat16, 16, true>, grid, threads, one_bytes, stream, a);
+      }
+    } else {
+      switch (rows_per_thread(rows)) {
+        case 4: hx_launch(state_space_scan_kernel<__nv_bfloat16, 4, false>, grid, threads, shared_bytes, stream, a); break;
+        case 8: hx_launch(state_space_scan_kernel<__nv_bfloat16, 8, false>, grid, threads, shared_bytes, stream, a); break;
+        default: hx_launch(state_space_scan_kernel<__nv_bfloat16, 16, false>, grid, threads, shared_bytes, stream, a);
+      }
     }
   } else {
     HX_REQUIRE(false, "hx_state_space_scan: unknown dtype %d", dtype);
@@ -602,9 +632,8 @@ HX_API int hx_outer_product_scan(const void* r, int ld_r, const void* k, int ld_
                                  int ld_v, int dtype, const float* decay_log, int ld_decay,
                                  const float* w0, const float* bonus, float* state,
                                  long long state_stride, int head_stride, float* o,
-                                 const int* request_start,
-                                 const int* request_slot, int requests, int heads, int dim,
-                                 cudaStream_t stream) {
+                                 const int* request_start, const int* request_slot, int requests,
+                                 int tokens, int heads, int dim, cudaStream_t stream) {
   HX_REQUIRE(requests >= 0 && heads > 0 && dim > 0, "hx_outer_product_scan: bad sizes");
   const int parts = parts_for(dim);
   HX_REQUIRE(parts > 0, "hx_outer_product_scan: heads of %d are more than %d", dim, 32 * 16);
@@ -620,15 +649,25 @@ HX_API int hx_outer_product_scan(const void* r, int ld_r, const void* k, int ld_
   if (requests == 0) return HX_OK;
   const dim3 grid(requests, heads, column_blocks);
   const size_t shared_bytes = static_cast<size_t>(tile) * per_token * sizeof(float);
+  const bool one_token = tokens == requests;
+  const size_t one_bytes = static_cast<size_t>(per_token) * sizeof(float);
   if (dtype == HX_F32) {
     OuterScanArgs<float> a{static_cast<const float*>(r), static_cast<const float*>(k),
                            static_cast<const float*>(v), ld_r, ld_k, ld_v, decay_log, ld_decay, w0,
                            bonus, state, state_stride, head_stride, o, request_start, request_slot,
                            heads, dim, parts, block_lanes, tile, per_token};
-    switch (rows_per_thread(dim)) {
-      case 4: hx_launch(outer_product_scan_kernel<float, 4>, grid, threads, shared_bytes, stream, a); break;
-      case 8: hx_launch(outer_product_scan_kernel<float, 8>, grid, threads, shared_bytes, stream, a); break;
-      default: hx_launch(outer_product_scan_kernel<float, 16>, grid, threads, shared_bytes, stream, a);
+    if (one_token) {
+      switch (rows_per_thread(dim)) {
+        case 4: hx_launch(outer_product_scan_kernel<float, 4, true>, grid, threads, one_bytes, stream, a); break;
+        case 8: hx_launch(outer_product_scan_kernel<float, 8, true>, grid, threads, one_bytes, stream, a); break;
+        default: hx_launch(outer_product_scan_kernel<float, 16, true>, grid, threads, one_bytes, stream, a);
+      }
+    } else {
+      switch (rows_per_thread(dim)) {
+        case 4: hx_launch(outer_product_scan_kernel<float, 4, false>, grid, threads, shared_bytes, stream, a); break;
+        case 8: hx_launch(outer_product_scan_kernel<float, 8, false>, grid, threads, shared_bytes, stream, a); break;
+        default: hx_launch(outer_product_scan_kernel<float, 16, false>, grid, threads, shared_bytes, stream, a);
+      }
     }
   } else if (dtype == HX_BF16) {
     OuterScanArgs<__nv_bfloat16> a{static_cast<const __nv_bfloat16*>(r),
@@ -637,10 +676,18 @@ HX_API int hx_outer_product_scan(const void* r, int ld_r, const void* k, int ld_
                                    decay_log, ld_decay, w0, bonus, state, state_stride,
                                    head_stride, o, request_start, request_slot, heads, dim, parts,
                                    block_lanes, tile, per_token};
-    switch (rows_per_thread(dim)) {
-      case 4: hx_launch(outer_product_scan_kernel<__nv_bfloat16, 4>, grid, threads, shared_bytes, stream, a); break;
-      case 8: hx_launch(outer_product_scan_kernel<__nv_bfloat16, 8>, grid, threads, shared_bytes, stream, a); break;
-      default: hx_launch(outer_product_scan_kernel<__nv_bfloat16, 16>, grid, threads, shared_bytes, stream, a);
+    if (one_token) {
+      switch (rows_per_thread(dim)) {
+        case 4: hx_launch(outer_product_scan_kernel<__nv_bfloat16, 4, true>, grid, threads, one_bytes, stream, a); break;
+        case 8: hx_launch(outer_product_scan_kernel<__nv_bfloat16, 8, true>, grid, threads, one_bytes, stream, a); break;
+        default: hx_launch(outer_product_scan_kernel<__nv_bfloat16, 16, true>, grid, threads, one_bytes, stream, a);
+      }
+    } else {
+      switch (rows_per_thread(dim)) {
+        case 4: hx_launch(outer_product_scan_kernel<__nv_bfloat16, 4, false>, grid, threads, shared_bytes, stream, a); break;
+        case 8: hx_launch(outer_product_scan_kernel<__nv_bfloat16, 8, false>, grid, threads, shared_bytes, stream, a); break;
+        default: hx_launch(outer_product_scan_kernel<__nv_bfloat16, 16, false>, grid, threads, shared_bytes, stream, a);
+      }
     }
   } else {
     HX_REQUIRE(false, "hx_outer_product_scan: unknown dtype %d", dtype);

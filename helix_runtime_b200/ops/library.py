@@ -144,14 +144,14 @@ def _declare(library: ctypes.CDLL) -> None:
     library.hx_state_space_scan.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int,
                                             _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_longlong, _c_int, _c_ptr,
                                             _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
-                                            _c_ptr]
+                                            _c_int, _c_ptr]
     library.hx_token_shift.argtypes = [_c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_longlong,
                                        _c_ptr, _c_longlong, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr,
                                        _c_ptr]
     library.hx_outer_product_scan.argtypes = [_c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int,
                                               _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_longlong,
                                               _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
-                                              _c_ptr]
+                                              _c_int, _c_ptr]
     library.hx_gated_group_norm.argtypes = [_c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr,
                                             _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr]
     library.hx_norm_rotary_append.argtypes = [
@@ -726,12 +726,13 @@ def state_space_scan(x: torch.Tensor, b: torch.Tensor, c: torch.Tensor, dt: torc
                      dt_bias: torch.Tensor, a_log: torch.Tensor, skip: torch.Tensor,
                      state: torch.Tensor, y: torch.Tensor, request_start: torch.Tensor,
                      request_slot: torch.Tensor, requests: int, heads: int, width: int, rows: int,
-                     groups: int) -> None:
+                     groups: int, tokens: Optional[int] = None) -> None:
     """The selective state-space recurrence over each request's tokens: per head
     ``S = exp(-exp(a_log) d) S + d B x'``, ``y = S' C + skip x`` with ``d = softplus(dt +
     dt_bias)``.  ``x`` ``[tokens, heads * width]``, ``b``, ``c`` ``[tokens, groups * rows]`` (views
     of one buffer), ``dt`` ``[tokens, heads]``; ``state`` ``[slots, >= heads * rows * width]`` and
-    ``y`` ``[tokens, heads * width]`` float32."""
+    ``y`` ``[tokens, heads * width]`` float32.  ``tokens`` (default: the rows of ``x``) is the
+    step's token count; when it equals ``requests`` the decode kernel runs."""
     for name, tensor in (("dt_bias", dt_bias), ("a_log", a_log), ("skip", skip), ("state", state),
                          ("y", y)):
         _need(tensor, torch.float32, name)
@@ -745,7 +746,8 @@ def state_space_scan(x: torch.Tensor, b: torch.Tensor, c: torch.Tensor, dt: torc
                                      dt_bias.data_ptr(), a_log.data_ptr(), skip.data_ptr(),
                                      state.data_ptr(), state.stride(0), head_stride, y.data_ptr(),
                                      request_start.data_ptr(), request_slot.data_ptr(), requests,
-                                     heads, width, rows, groups, _stream()))
+                                     x.shape[0] if tokens is None else tokens, heads, width, rows,
+                                     groups, _stream()))
 
 
 def token_shift(h: torch.Tensor, mu: torch.Tensor, out: torch.Tensor, state: torch.Tensor,
@@ -768,7 +770,7 @@ def token_shift(h: torch.Tensor, mu: torch.Tensor, out: torch.Tensor, state: tor
 def outer_product_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_log: torch.Tensor,
                        w0: torch.Tensor, bonus: torch.Tensor, state: torch.Tensor, o: torch.Tensor,
                        request_start: torch.Tensor, request_slot: torch.Tensor, requests: int,
-                       heads: int, dim: int) -> None:
+                       heads: int, dim: int, tokens: Optional[int] = None) -> None:
     """Per head ``o = (S + diag(bonus) k v')' r`` then ``S = diag(w) S + k v'`` with
     ``w = exp(-exp(decay_log + w0))``; ``r``, ``k``, ``v`` ``[tokens, heads * dim]`` in the compute
     dtype, ``decay_log`` and ``o`` float32, ``state`` ``[slots, >= heads * scan_state_floats(dim,
@@ -784,7 +786,9 @@ def outer_product_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_
                                        decay_log.data_ptr(), decay_log.stride(0), w0.data_ptr(),
                                        bonus.data_ptr(), state.data_ptr(), state.stride(0),
                                        head_stride, o.data_ptr(), request_start.data_ptr(),
-                                       request_slot.data_ptr(), requests, heads, dim, _stream()))
+                                       request_slot.data_ptr(), requests,
+                                       r.shape[0] if tokens is None else tokens, heads, dim,
+                                       _stream()))
 
 
 def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,

@@ -123,7 +123,7 @@ class StateSpaceMixer(Mixer):
                              self.dt_bias, self.a_log, self.skip,
                              _state_piece(cache, self.filter_state, self.matrix_state), y,
                              ctx.request_start, ctx.request_slot, ctx.n_requests, self.heads,
-                             self.head_width, self.state_size, self.groups)
+                             self.head_width, self.state_size, self.groups, tokens=n)
         ops.gated_group_norm(y, rows[:, :inner], self.norm, gated, n, self.norm_groups, self.eps,
                              gate_after=False)
         project(gated, self.w_o, residual, n, ops.EPI_ADD_F32, ctx.status, ctx.ordered_sums)
@@ -195,7 +195,7 @@ class TimeMix(Mixer):
         ops.outer_product_scan(projected[0], projected[1], projected[2], decay_log, self.w0,
                                self.bonus, _state_piece(cache, h, self.matrix_state), o,
                                ctx.request_start, ctx.request_slot, ctx.n_requests, self.heads,
-                               self.head_dim)
+                               self.head_dim, tokens=n)
         ops.gated_group_norm(o, projected[3], self.norm, normed, n, self.heads, self.eps,
                              gate_after=True)
         project(normed, self.weights["o"], residual, n, ops.EPI_ADD_F32, ctx.status,

@@ -143,12 +143,14 @@ int hx_causal_filter(const void* raw, int ld_raw, void* out, int ld_out, int dty
 /* floats that a head's rows x columns matrix takes in a state row (the kernels' own order) */
 int hx_scan_state_floats(int columns, int rows);
 /* per head: S = exp(-exp(a_log) d) S + d B x', y = S' C + skip x, d = softplus(dt + dt_bias);
- * state: heads x head_stride floats; y float32 [tokens][heads * width] */
+ * state: heads x head_stride floats; y float32 [tokens][heads * width]; tokens == requests
+ * (a decode step) takes the kernel built for one token per request */
 int hx_state_space_scan(const void* x, const void* b, const void* c, int ld, const void* dt,
                         int ld_dt, int dtype, const float* dt_bias, const float* a_log,
                         const float* skip, float* state, long long state_stride, int head_stride,
                         float* y, const int* request_start, const int* request_slot, int requests,
-                        int heads, int width, int rows, int groups, cudaStream_t stream);
+                        int tokens, int heads, int width, int rows, int groups,
+                        cudaStream_t stream);
 /* out[s][t] = h[t] + (h[t-1] - h[t]) * mu[s]; the state row [hidden] is the previous step's
  * last row and becomes this step's */
 int hx_token_shift(const void* h, int ld, int dtype, const float* mu, int mixes, void* out,
@@ -162,7 +164,7 @@ int hx_outer_product_scan(const void* r, int ld_r, const void* k, int ld_k, cons
                           const float* w0, const float* bonus, float* state,
                           long long state_stride, int head_stride, float* o,
                           const int* request_start,
-                          const int* request_slot, int requests, int heads, int dim,
+                          const int* request_slot, int requests, int tokens, int heads, int dim,
                           cudaStream_t stream);
 /* channels in `groups` equal parts, each over its root mean square, times weight; the gate
  * silu(gate) multiplies before the norm (gate_after 0) or after it (1) */
