@@ -124,7 +124,8 @@ class ComputedRotary(PositionEncoding):
     positions), with three optional companions in the same kernel.
 
     Parameters: ``theta``, ``head_dim``, ``rotary_dim`` (default: all of the head; 0: none),
-    ``row_dim`` (default ``head_dim``), ``pairing`` (``half_split``: ``(m, m + rotary_dim/2)``,
+    ``row_dim`` (default: the larger of ``head_dim`` and ``value_dim``), ``pairing``
+    (``half_split``: ``(m, m + rotary_dim/2)``,
     the default; ``adjacent``: ``(2m, 2m + 1)``).  The angle of pair ``m`` at position ``p`` is
     the float32 product ``p * f[m]`` with ``f[m] = theta^(-2m / rotary_dim)`` rounded to float32
     once; sine and cosine are float32.
@@ -143,8 +144,8 @@ class ComputedRotary(PositionEncoding):
         self.theta = float(spec["theta"])
         self.head_dim = int(spec["head_dim"])
         self.rotary_dim = int(spec.get("rotary_dim", self.head_dim))
-        self.row_dim = int(spec.get("row_dim", self.head_dim))
         self.value_dim = int(spec.get("value_dim", self.head_dim))
+        self.row_dim = int(spec.get("row_dim", max(self.head_dim, self.value_dim)))
         if self.row_dim < max(self.head_dim, self.value_dim):
             raise ValueError("row_dim must hold the head and its values")
         pairing = spec.get("pairing", "half_split")
