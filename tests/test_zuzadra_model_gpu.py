@@ -18,8 +18,8 @@ from zuzadra_configs import CONFIGS, PAGE_SIZE, make_folder
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"streams3": (1, 2, 9, 33, 90), "single": (3, 17, 40, 75), "fast": (5, 70, 150, 260),
-           "odd": (4, 11, 50, 100)}
-NAMES = ("streams3", "single", "fast", "odd")
+           "odd": (4, 11, 50, 100), "recurrent": (2, 19, 60, 121)}
+NAMES = ("streams3", "single", "fast", "odd", "recurrent")
 CASES = [(name, dtype) for dtype in ("float32", "bfloat16") for name in NAMES]
 # float32: double against float32 sums and recurrences.  bfloat16: the plain implementation
 # rounds where the engine stores; what is left are activations that fall on the other side of
@@ -156,6 +156,7 @@ def test_mixed_batches_over_a_small_pool(name, dtype, seed, models, expectations
     replay(harness, steps, expectations(name, dtype, 30), dtype, f"{name} {dtype} mixed")
     stats = harness.cache.stats()
     assert all(group["reuses"] > 0 for group in stats["groups"]), "no page was used again"
+    assert stats["groups"] or name == "recurrent"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -13,6 +13,9 @@ They differ in every size and constant, and inside a model the layers differ too
 * ``fast``: the shapes the tensor-core kernels take (width 256, heads of 64, feed-forward 512),
   two streams, sharp attention (scores spread by about six) over a window of 40, prompts of
   hundreds of tokens, the parallel layer run twice.
+* ``recurrent``: state-space layers only (no keys or values anywhere, so the cache manager has
+  no pages to hand out), one residual stream WITH connection weights, a state of one row in its
+  second layer, the first layer run twice.
 * ``odd``: sizes no fast kernel takes: width 90, five streams, heads of 20 with values of 12, a
   time-mix head of 12 (three heads), a decay rank of 5, a filter of five taps, an odd
   vocabulary, one stream count that is no power of two, a loop that runs once.
@@ -74,6 +77,12 @@ CONFIGS = {
                    _layer(_ssm(4, 64, 32, conv=4), 512)],
         "loop": {"start": 1, "stop": 2, "times": 2},
     },
+    "recurrent": {
+        "architecture": "Zuzadra", "vocab": 150, "width": 48, "norm": {"eps": 1e-5}, "streams": 1,
+        "layers": [_layer(_ssm(3, 8, 12, conv=3), 64),
+                   _layer(_ssm(2, 16, 1, groups=2, conv=2, norm_groups=2), None)],
+        "loop": {"start": 0, "stop": 1, "times": 2},
+    },
     "odd": {
         "architecture": "Zuzadra", "vocab": 131, "width": 90, "norm": {"eps": 1e-4}, "streams": 5,
         "layers": [_layer(_parallel(3, 3, 20, 12, 33, 10, 77.0, 3, 12, 1.5, 0.4), 70),
@@ -81,9 +90,9 @@ CONFIGS = {
         "loop": {"start": 1, "stop": 2, "times": 1},
     },
 }
-PAGE_SIZE = {"streams3": 8, "single": 16, "fast": 16, "odd": 8}
-SEED = {"streams3": 21, "single": 22, "fast": 23, "odd": 24}
-DECAY_RANK = {"streams3": 8, "single": 16, "fast": 32, "odd": 5}
+PAGE_SIZE = {"streams3": 8, "single": 16, "fast": 16, "odd": 8, "recurrent": 16}
+SEED = {"streams3": 21, "single": 22, "fast": 23, "odd": 24, "recurrent": 25}
+DECAY_RANK = {"streams3": 8, "single": 16, "fast": 32, "odd": 5, "recurrent": 1}
 
 
 def tensors_for(config: dict, seed: int, storage_dtype: torch.dtype, decay_rank: int):
