@@ -37,14 +37,15 @@ __global__ void streams_spread_kernel(const float* __restrict__ x, float* __rest
 
 // One block per output row.  `rows` gathers (the final norm runs on the wanted rows only);
 // `clear`, when given, is the float32 row [hidden] that the sublayer will sum its output into:
-// it is zeroed here (row index = the token, not the gathered one).  COUNT > 0: the number of
+// it is zeroed here, or set to `initial` [hidden] (a bias the sublayer's output starts from);
+// row index = the token, not the gathered one.  COUNT > 0: the number of
 // streams is known to the compiler; VECTORS > 0: the width is a multiple of four and a thread
 // keeps up to VECTORS float4 of the weighted sum, so the streams are read once.
 template <typename TOut, int COUNT, int VECTORS>
 __global__ __launch_bounds__(256) void streams_read_norm_kernel(
     const float* __restrict__ streams, const float* __restrict__ read, int count_arg,
     const float* __restrict__ weight, TOut* __restrict__ out, float* __restrict__ clear,
-    const int* __restrict__ rows, int hidden, float eps) {
+    const float* __restrict__ initial, const int* __restrict__ rows, int hidden, float eps) {
   __shared__ float scratch[32];
   __shared__ float a[MAX_STREAMS];
   const int count = COUNT > 0 ? COUNT : count_arg;
@@ -94,7 +95,8 @@ __global__ __launch_bounds__(256) void streams_read_norm_kernel(
         yr[c + 3] = hx_from_float<TOut>(u[i].w * inverse * w.w);
         if (clear != nullptr)
           reinterpret_cast<float4*>(clear + static_cast<size_t>(out_row) * hidden)[v] =
-              make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+              initial != nullptr ? reinterpret_cast<const float4*>(initial)[v]
+                                 : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
       }
     }
   } else {
@@ -109,7 +111,8 @@ __global__ __launch_bounds__(256) void streams_read_norm_kernel(
       float u = 0.0f;
       for (int s = 0; s < count; ++s) u = fmaf(a[s], base[static_cast<size_t>(s) * hidden + c], u);
       yr[c] = hx_from_float<TOut>(u * inverse * weight[c]);
-      if (clear != nullptr) clear[static_cast<size_t>(out_row) * hidden + c] = 0.0f;
+      if (clear != nullptr)
+        clear[static_cast<size_t>(out_row) * hidden + c] = initial != nullptr ? initial[c] : 0.0f;
     }
   }
 }
@@ -266,8 +269,8 @@ HX_API int hx_streams_spread(const float* x, float* streams, int tokens, int hid
 
 HX_API int hx_streams_read_norm(const float* streams, const float* read, int count,
                                 const float* weight, void* out, int out_dtype, float* clear,
-                                const int* rows, int n_rows, int hidden, float eps,
-                                cudaStream_t stream) {
+                                const float* initial, const int* rows, int n_rows, int hidden,
+                                float eps, cudaStream_t stream) {
   HX_REQUIRE(n_rows >= 0 && hidden > 0, "hx_streams_read_norm: bad sizes");
   HX_REQUIRE(count >= 1 && count <= MAX_STREAMS, "hx_streams_read_norm: 1 to %d streams",
              MAX_STREAMS);
@@ -276,11 +279,12 @@ HX_API int hx_streams_read_norm(const float* streams, const float* read, int cou
   HX_REQUIRE(out_dtype == HX_F32 || out_dtype == HX_BF16,
              "hx_streams_read_norm: unknown dtype %d", out_dtype);
   const bool aligned = ((reinterpret_cast<uintptr_t>(streams) | reinterpret_cast<uintptr_t>(weight) |
-                         reinterpret_cast<uintptr_t>(clear)) & 15) == 0;
+                         reinterpret_cast<uintptr_t>(clear) | reinterpret_cast<uintptr_t>(initial)) &
+                        15) == 0;
   const bool vector = hidden % 4 == 0 && hidden <= 4 * 256 * 8 && aligned;
 #define HX_READ_NORM(T, COUNT, VECTORS)                                                        \
   hx_launch(streams_read_norm_kernel<T, COUNT, VECTORS>, n_rows, 256, 0, stream, streams, read, \
-            count, weight, static_cast<T*>(out), clear, rows, hidden, eps)
+            count, weight, static_cast<T*>(out), clear, initial, rows, hidden, eps)
 #define HX_READ_NORM_COUNT(T, VECTORS)                   \
   switch (count) {                                       \
     case 1: HX_READ_NORM(T, 1, VECTORS); break;          \

@@ -70,9 +70,15 @@ def _streams(block: "Block", ctx: StepContext, cache: LayerCache, residual: torc
     block.mixer.forward(ctx, cache, normed, output)
     block.mixer_connection.write_back(ctx, residual, output)
     if block.feed_forward is not None:
+        # a feed-forward whose output has a bias lets the buffer start from it (output_bias)
+        # instead of adding it in a pass of its own
+        bias = getattr(block.feed_forward, "output_bias", None)
         block.feed_forward_connection.read_normed(ctx, block.feed_forward_norm, residual, normed,
-                                                  output)
-        block.feed_forward.forward(ctx, normed, output)
+                                                  output, initial=bias)
+        if bias is None:
+            block.feed_forward.forward(ctx, normed, output)
+        else:
+            block.feed_forward.forward(ctx, normed, output, bias_in_place=True)
         block.feed_forward_connection.write_back(ctx, residual, output)
 
 

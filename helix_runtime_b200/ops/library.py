@@ -129,7 +129,7 @@ def _declare(library: ctypes.CDLL) -> None:
     library.hx_bounded_wait_check.restype = _c_int
     library.hx_streams_spread.argtypes = [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr]
     library.hx_streams_read_norm.argtypes = [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr,
-                                             _c_ptr, _c_int, _c_int, _c_float, _c_ptr]
+                                             _c_ptr, _c_ptr, _c_int, _c_int, _c_float, _c_ptr]
     library.hx_streams_write.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
                                          _c_int, _c_ptr]
     library.hx_scaled_sum.argtypes = [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr]
@@ -594,10 +594,12 @@ def streams_spread(x: torch.Tensor, streams: torch.Tensor, tokens: int, count: i
 def streams_read_norm(streams: torch.Tensor, read: Optional[torch.Tensor], count: int,
                       weight: torch.Tensor, out: torch.Tensor, eps: float, n_rows: int,
                       clear: Optional[torch.Tensor] = None,
-                      rows: Optional[torch.Tensor] = None) -> None:
+                      rows: Optional[torch.Tensor] = None,
+                      initial: Optional[torch.Tensor] = None) -> None:
     """out[r] = rmsnorm(sum_s read[s] * streams[r', s]) * weight with r' = rows[r] or r
     (``read`` None: every stream counts once).  ``clear`` (float32 ``[rows, hidden]``): its
-    first ``n_rows`` rows are zeroed, for the sublayer to sum its output into."""
+    first ``n_rows`` rows are zeroed, for the sublayer to sum its output into, or set to
+    ``initial`` (float32 ``[hidden]``: a bias that output starts from)."""
     _need(streams, torch.float32, "streams")
     _need(weight, torch.float32, "weight")
     hidden = weight.shape[0]
@@ -611,9 +613,13 @@ def streams_read_norm(streams: torch.Tensor, read: Optional[torch.Tensor], count
         assert clear.is_contiguous() and clear.shape[1] == hidden and rows is None
     if rows is not None:
         _need(rows, torch.int32, "rows")
+    if initial is not None:
+        _need(initial, torch.float32, "initial")
+        assert clear is not None and initial.numel() == hidden and initial.is_contiguous()
     _check(lib().hx_streams_read_norm(streams.data_ptr(), _ptr(read), count, weight.data_ptr(),
                                       out.data_ptr(), dtype_code(out.dtype), _ptr(clear),
-                                      _ptr(rows), n_rows, hidden, float(eps), _stream()))
+                                      _ptr(initial), _ptr(rows), n_rows, hidden, float(eps),
+                                      _stream()))
 
 
 def streams_write(streams: torch.Tensor, y: torch.Tensor, mixing: Optional[torch.Tensor],

@@ -63,9 +63,11 @@ class StreamConnection(Part):
                     + (self.hidden_size if self.layer_scale else 0))
 
     def read_normed(self, ctx: StepContext, norm: Norm, streams: torch.Tensor, normed: torch.Tensor,
-                    output: torch.Tensor) -> None:
-        """``normed[:n] = norm(sum_s a[s] X[s])``; ``output[:n]`` is zeroed for the sublayer."""
-        norm.forward_streams(ctx, streams, self.streams, self.read, normed, clear=output)
+                    output: torch.Tensor, initial: Optional[torch.Tensor] = None) -> None:
+        """``normed[:n] = norm(sum_s a[s] X[s])``; ``output[:n]`` is zeroed for the sublayer, or
+        set to ``initial`` (a bias of the sublayer's output, ``[hidden]`` float32)."""
+        norm.forward_streams(ctx, streams, self.streams, self.read, normed, clear=output,
+                             initial=initial)
 
     def write_back(self, ctx: StepContext, streams: torch.Tensor, output: torch.Tensor) -> None:
         ops.streams_write(streams, output, self.mixing, self.write, self.scale, self.streams,

@@ -104,7 +104,14 @@ class DenseMlp(FeedForward):
     def weight_bytes(self) -> int:
         return self.w_up.nbytes() + self.w_down.nbytes()
 
-    def forward(self, ctx: StepContext, x: torch.Tensor, residual: torch.Tensor) -> None:
+    @property
+    def output_bias(self) -> Optional[torch.Tensor]:
+        """The bias of the second projection, ``[hidden]`` float32: a caller that owns the buffer
+        this part sums into may let the buffer start from it and say so (``bias_in_place``)."""
+        return self.down_bias
+
+    def forward(self, ctx: StepContext, x: torch.Tensor, residual: torch.Tensor,
+                bias_in_place: bool = False) -> None:
         n = ctx.n_tokens
         sums = ctx.workspace.get(f"mlp.up/{self.intermediate}", (ctx.capacity, self.intermediate),
                                  torch.float32)
@@ -112,7 +119,7 @@ class DenseMlp(FeedForward):
                                 ctx.dtype)
         project(x, self.w_up, sums, n, ops.EPI_STORE_F32, ctx.status)
         ops.biased_activation(sums, self.up_bias, act, n, ops.ACT_XIELU, *self.constants)
-        if self.down_bias is not None:
+        if self.down_bias is not None and not bias_in_place:
             ops.add_bias(residual, self.down_bias, n)
         project(act, self.w_down, residual, n, ops.EPI_ADD_F32, ctx.status, ctx.ordered_sums)
 

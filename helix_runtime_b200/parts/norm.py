@@ -46,12 +46,14 @@ class RmsNorm(Norm):
     def forward_streams(self, ctx: StepContext, streams: torch.Tensor, count: int,
                         read: Optional[torch.Tensor], out: torch.Tensor,
                         clear: Optional[torch.Tensor] = None,
-                        rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> None:
+                        rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None,
+                        initial: Optional[torch.Tensor] = None) -> None:
         """The norm of ``sum_s read[s] * streams[:, s]`` (``read`` None: the plain sum) for
         ``streams`` ``[rows, count * hidden]``; ``clear``: a float32 buffer whose rows are zeroed
-        on the way (the sublayer sums its output into it)."""
+        on the way (the sublayer sums its output into it), or set to ``initial`` ``[hidden]``."""
         ops.streams_read_norm(streams, read, count, self.weight, out, self.eps,
-                              ctx.n_tokens if n_rows is None else n_rows, clear=clear, rows=rows)
+                              ctx.n_tokens if n_rows is None else n_rows, clear=clear, rows=rows,
+                              initial=initial)
 
 
 class LayerNorm(Norm):

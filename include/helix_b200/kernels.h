@@ -113,10 +113,11 @@ int hx_short_conv_append(const void* raw, int ld_raw, const float* accum, int ld
 int hx_streams_spread(const float* x, float* streams, int tokens, int hidden, int count,
                       cudaStream_t stream);
 /* out[r] = rmsnorm(sum_s read[s] * streams[rows ? rows[r] : r][s]) * weight (read NULL: ones);
- * clear (may be NULL): float32 rows [n_rows, hidden] that are zeroed */
+ * clear (may be NULL): float32 rows [n_rows, hidden] that are zeroed, or set to initial [hidden]
+ * when that is given */
 int hx_streams_read_norm(const float* streams, const float* read, int count, const float* weight,
-                         void* out, int out_dtype, float* clear, const int* rows, int n_rows,
-                         int hidden, float eps, cudaStream_t stream);
+                         void* out, int out_dtype, float* clear, const float* initial,
+                         const int* rows, int n_rows, int hidden, float eps, cudaStream_t stream);
 /* streams[t][r] = sum_s mixing[s][r] * streams[t][s] + write[r] * scale[c] * y[t][c], all r at
  * once from the old streams (mixing, write, scale NULL: ones) */
 int hx_streams_write(float* streams, const float* y, const float* mixing, const float* write,

@@ -64,6 +64,12 @@ def test_streams_read_norm_and_write(streams, dtype):
     want = plain.rms_norm_one_plus(u, weight, eps)
     close(as_double(out), want, 1e-5 if dtype == torch.float32 else 4e-2, 1e-5)
     assert float(clear.abs().max()) == 0.0
+    # the cleared buffer may start from a vector (a bias) instead of zero
+    start = rng.normal(size=hidden)
+    ops.streams_read_norm(d_streams, device_tensor(read), streams, device_tensor(1.0 + weight), out,
+                          eps, tokens, clear=clear, initial=device_tensor(start))
+    close(as_double(clear), np.tile(start.astype(np.float32), (tokens, 1)), 0.0)
+    close(as_double(out), want, 1e-5 if dtype == torch.float32 else 4e-2, 1e-5)
     # gathered rows, plain sum of the streams (the final norm)
     rows = torch.tensor([5, 0, 5], dtype=torch.int32, device="cuda")
     gathered = torch.empty((3, hidden), dtype=dtype, device="cuda")
