@@ -40,6 +40,22 @@ __device__ __forceinline__ float softplus(float x) {
   return x > 20.0f ? x : log1pf(expf(x));
 }
 
+// One step S <- decay * S + add of a recurrence in the float32 engine.  A decay close to one
+// cannot be told from its neighbours in float32 (their spacing is 6e-8), and a head that hardly
+// forgets multiplies a thousand such decays over a long prompt: the roundings add up like a
+// random walk and show in the logits of late positions.  So the decay arrives as d = decay - 1
+// (taken with expm1f, which keeps its digits), the step is S + (d S + add), and the rounding of
+// that sum (a two-sum recovers it) is carried beside S in `carry`, which decays like S.  What
+// reads the state reads S + carry; the state row holds S + carry rounded once.
+__device__ __forceinline__ void decayed_add_exact(float& S, float& carry, float d, float add) {
+  const float t = fmaf(d, S, add);
+  const float sum = S + t;
+  const float shadow = sum - S;
+  const float error = (S - (sum - shadow)) + (t - shadow);
+  carry = fmaf(d, carry, carry) + error;
+  S = sum;
+}
+
 // ---------------------------------------------------------------- filter, bias, silu
 
 template <typename T>
@@ -193,6 +209,7 @@ template <typename T, int ROWS_PER_THREAD, bool ONE_TOKEN>
 __global__ __launch_bounds__(SCAN_THREADS, ONE_TOKEN ? 3 : HX_SCAN_CTAS)
 void state_space_scan_kernel(const ScanArgs<T> a) {
   constexpr int STRIDE = run_stride<ROWS_PER_THREAD>();
+  constexpr bool EXACT = sizeof(T) == 4;      // the float32 engine, see decayed_add_exact
   extern __shared__ float4 shared4[];
   float* shared = reinterpret_cast<float*>(shared4);
   hx_pdl_prologue();
@@ -215,10 +232,12 @@ void state_space_scan_kernel(const ScanArgs<T> a) {
   float* s_state = a.state + static_cast<size_t>(a.request_slot[request]) * a.state_stride +
                    static_cast<size_t>(head) * a.head_stride;
   float S[ROWS_PER_THREAD];
+  float carry[EXACT ? ROWS_PER_THREAD : 1];
 #pragma unroll
   for (int k = 0; k < ROWS_PER_THREAD; ++k) {
     const int n = part * ROWS_PER_THREAD + k;
     S[k] = (live && n < rows) ? s_state[static_cast<size_t>(k) * lanes + lane] : 0.0f;
+    carry[EXACT ? k : 0] = 0.0f;
   }
   // rows the matrix does not have stay zero in the staged vectors: nothing is guarded below
   for (int i = threadIdx.x; i < (ONE_TOKEN ? 1 : a.tile) * per_token; i += blockDim.x)
@@ -243,7 +262,7 @@ void state_space_scan_kernel(const ScanArgs<T> a) {
     for (int t = threadIdx.x; t < here; t += blockDim.x) {
       const float step = softplus(hx_to_float<T>(a.dt[(first + t) * a.ld_dt + head]) + bias);
       shared[t * per_token + 2 * run + width] = step;
-      shared[t * per_token + 2 * run + width + 1] = expf(-rate * step);
+      shared[t * per_token + 2 * run + width + 1] = EXACT ? expm1f(-rate * step) : expf(-rate * step);
     }
     __syncthreads();
     float* y_out = a.y + first * (a.heads * width) + head * width + column;
@@ -261,14 +280,25 @@ void state_space_scan_kernel(const ScanArgs<T> a) {
       for (int q = 0; q < ROWS_PER_THREAD / 4; ++q) {
         const float4 bv = b4[q];
         const float4 cv = c4[q];
-        S[4 * q + 0] = fmaf(decay, S[4 * q + 0], bv.x * push);
-        S[4 * q + 1] = fmaf(decay, S[4 * q + 1], bv.y * push);
-        S[4 * q + 2] = fmaf(decay, S[4 * q + 2], bv.z * push);
-        S[4 * q + 3] = fmaf(decay, S[4 * q + 3], bv.w * push);
-        sum0 = fmaf(S[4 * q + 0], cv.x, sum0);
-        sum1 = fmaf(S[4 * q + 1], cv.y, sum1);
-        sum0 = fmaf(S[4 * q + 2], cv.z, sum0);
-        sum1 = fmaf(S[4 * q + 3], cv.w, sum1);
+        if constexpr (EXACT) {       // `decay` holds decay - 1 here
+          decayed_add_exact(S[4 * q + 0], carry[4 * q + 0], decay, bv.x * push);
+          decayed_add_exact(S[4 * q + 1], carry[4 * q + 1], decay, bv.y * push);
+          decayed_add_exact(S[4 * q + 2], carry[4 * q + 2], decay, bv.z * push);
+          decayed_add_exact(S[4 * q + 3], carry[4 * q + 3], decay, bv.w * push);
+          sum0 = fmaf(S[4 * q + 0] + carry[4 * q + 0], cv.x, sum0);
+          sum1 = fmaf(S[4 * q + 1] + carry[4 * q + 1], cv.y, sum1);
+          sum0 = fmaf(S[4 * q + 2] + carry[4 * q + 2], cv.z, sum0);
+          sum1 = fmaf(S[4 * q + 3] + carry[4 * q + 3], cv.w, sum1);
+        } else {
+          S[4 * q + 0] = fmaf(decay, S[4 * q + 0], bv.x * push);
+          S[4 * q + 1] = fmaf(decay, S[4 * q + 1], bv.y * push);
+          S[4 * q + 2] = fmaf(decay, S[4 * q + 2], bv.z * push);
+          S[4 * q + 3] = fmaf(decay, S[4 * q + 3], bv.w * push);
+          sum0 = fmaf(S[4 * q + 0], cv.x, sum0);
+          sum1 = fmaf(S[4 * q + 1], cv.y, sum1);
+          sum0 = fmaf(S[4 * q + 2], cv.z, sum0);
+          sum1 = fmaf(S[4 * q + 3], cv.w, sum1);
+        }
       }
       float sum = sum0 + sum1;
       for (int offset = parts >> 1; offset > 0; offset >>= 1)
@@ -280,7 +310,8 @@ void state_space_scan_kernel(const ScanArgs<T> a) {
 #pragma unroll
     for (int k = 0; k < ROWS_PER_THREAD; ++k) {
       const int n = part * ROWS_PER_THREAD + k;
-      if (n < rows) s_state[static_cast<size_t>(k) * lanes + lane] = S[k];
+      if (n < rows)
+        s_state[static_cast<size_t>(k) * lanes + lane] = EXACT ? S[k] + carry[EXACT ? k : 0] : S[k];
     }
   }
 }
@@ -344,6 +375,7 @@ template <typename T, int ROWS_PER_THREAD, bool ONE_TOKEN>
 __global__ __launch_bounds__(SCAN_THREADS, ONE_TOKEN ? 3 : HX_SCAN_CTAS)
 void outer_product_scan_kernel(const OuterScanArgs<T> a) {
   constexpr int STRIDE = run_stride<ROWS_PER_THREAD>();
+  constexpr bool EXACT = sizeof(T) == 4;      // the float32 engine, see decayed_add_exact
   extern __shared__ float4 shared4[];
   float* shared = reinterpret_cast<float*>(shared4);
   hx_pdl_prologue();
@@ -364,10 +396,12 @@ void outer_product_scan_kernel(const OuterScanArgs<T> a) {
   float* s_state = a.state + static_cast<size_t>(a.request_slot[request]) * a.state_stride +
                    static_cast<size_t>(head) * a.head_stride;
   float S[ROWS_PER_THREAD];
+  float carry[EXACT ? ROWS_PER_THREAD : 1];
 #pragma unroll
   for (int i = 0; i < ROWS_PER_THREAD; ++i) {
     const int n = part * ROWS_PER_THREAD + i;
     S[i] = (live && n < dim) ? s_state[static_cast<size_t>(i) * lanes + lane] : 0.0f;
+    carry[EXACT ? i : 0] = 0.0f;
   }
   for (int i = threadIdx.x; i < (ONE_TOKEN ? 1 : a.tile) * per_token; i += blockDim.x)
     shared[i] = 0.0f;
@@ -388,7 +422,8 @@ void outer_product_scan_kernel(const OuterScanArgs<T> a) {
           [&](int t, int e) { return hx_to_float<T>(k[static_cast<size_t>(t) * a.ld_k + e]); }, padded<ROWS_PER_THREAD>);
     stage<ONE_TOKEN>(shared + 2 * run, per_token, here, dim,
           [&](int t, int e) {
-            return expf(-expf(decay_log[static_cast<size_t>(t) * a.ld_decay + e] + w0[e]));
+            const float rate = expf(decay_log[static_cast<size_t>(t) * a.ld_decay + e] + w0[e]);
+            return EXACT ? expm1f(-rate) : expf(-rate);
           },
           padded<ROWS_PER_THREAD>);
     stage<ONE_TOKEN>(shared + 3 * run, per_token, here, dim,
@@ -417,14 +452,25 @@ void outer_product_scan_kernel(const OuterScanArgs<T> a) {
         const float4 wv = w4[q];
         const float4 uv = u4[q];          // bonus * k
         const float p0 = kv.x * vj, p1 = kv.y * vj, p2 = kv.z * vj, p3 = kv.w * vj;
-        sum0 = fmaf(rv.x, fmaf(uv.x, vj, S[4 * q + 0]), sum0);
-        sum1 = fmaf(rv.y, fmaf(uv.y, vj, S[4 * q + 1]), sum1);
-        sum0 = fmaf(rv.z, fmaf(uv.z, vj, S[4 * q + 2]), sum0);
-        sum1 = fmaf(rv.w, fmaf(uv.w, vj, S[4 * q + 3]), sum1);
-        S[4 * q + 0] = fmaf(wv.x, S[4 * q + 0], p0);
-        S[4 * q + 1] = fmaf(wv.y, S[4 * q + 1], p1);
-        S[4 * q + 2] = fmaf(wv.z, S[4 * q + 2], p2);
-        S[4 * q + 3] = fmaf(wv.w, S[4 * q + 3], p3);
+        if constexpr (EXACT) {       // `wv` holds the decays minus one here
+          sum0 = fmaf(rv.x, fmaf(uv.x, vj, S[4 * q + 0] + carry[4 * q + 0]), sum0);
+          sum1 = fmaf(rv.y, fmaf(uv.y, vj, S[4 * q + 1] + carry[4 * q + 1]), sum1);
+          sum0 = fmaf(rv.z, fmaf(uv.z, vj, S[4 * q + 2] + carry[4 * q + 2]), sum0);
+          sum1 = fmaf(rv.w, fmaf(uv.w, vj, S[4 * q + 3] + carry[4 * q + 3]), sum1);
+          decayed_add_exact(S[4 * q + 0], carry[4 * q + 0], wv.x, p0);
+          decayed_add_exact(S[4 * q + 1], carry[4 * q + 1], wv.y, p1);
+          decayed_add_exact(S[4 * q + 2], carry[4 * q + 2], wv.z, p2);
+          decayed_add_exact(S[4 * q + 3], carry[4 * q + 3], wv.w, p3);
+        } else {
+          sum0 = fmaf(rv.x, fmaf(uv.x, vj, S[4 * q + 0]), sum0);
+          sum1 = fmaf(rv.y, fmaf(uv.y, vj, S[4 * q + 1]), sum1);
+          sum0 = fmaf(rv.z, fmaf(uv.z, vj, S[4 * q + 2]), sum0);
+          sum1 = fmaf(rv.w, fmaf(uv.w, vj, S[4 * q + 3]), sum1);
+          S[4 * q + 0] = fmaf(wv.x, S[4 * q + 0], p0);
+          S[4 * q + 1] = fmaf(wv.y, S[4 * q + 1], p1);
+          S[4 * q + 2] = fmaf(wv.z, S[4 * q + 2], p2);
+          S[4 * q + 3] = fmaf(wv.w, S[4 * q + 3], p3);
+        }
       }
       float sum = sum0 + sum1;
       for (int offset = parts >> 1; offset > 0; offset >>= 1)
@@ -436,7 +482,8 @@ void outer_product_scan_kernel(const OuterScanArgs<T> a) {
 #pragma unroll
     for (int i = 0; i < ROWS_PER_THREAD; ++i) {
       const int n = part * ROWS_PER_THREAD + i;
-      if (n < dim) s_state[static_cast<size_t>(i) * lanes + lane] = S[i];
+      if (n < dim)
+        s_state[static_cast<size_t>(i) * lanes + lane] = EXACT ? S[i] + carry[EXACT ? i : 0] : S[i];
     }
   }
 }
