@@ -143,6 +143,9 @@ constexpr int SCAN_THREADS = 256;
 #ifndef HX_SCAN_CTAS
 #define HX_SCAN_CTAS 2
 #endif
+#ifndef HX_SCAN_TILE_KB
+#define HX_SCAN_TILE_KB 24
+#endif
 
 template <typename T>
 struct ScanArgs {
@@ -543,9 +546,10 @@ int staged_floats(int vectors, int rows, int plain) {
   return (vectors * parts_for(rows) * (rpt + (rpt >= 8 ? 4 : 0)) + plain + 3) / 4 * 4;
 }
 
-// tokens staged per tile: a tile of at most 24 KB, so that several CTAs share an SM
+// tokens staged per tile: a tile of at most HX_SCAN_TILE_KB kilobytes (below the 48 KB a CTA gets
+// without asking), so that several CTAs share an SM
 int tile_for(int floats_per_token) {
-  const int budget = 24 * 1024 / 4;
+  const int budget = HX_SCAN_TILE_KB * 1024 / 4;
   int tile = budget / floats_per_token;
   if (tile > 32) tile = 32;
   return tile;
