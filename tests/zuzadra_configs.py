@@ -11,7 +11,7 @@ They differ in every size and constant, and inside a model the layers differ too
   a page, scales of one; a state-space layer with a filter of one tap (none) and a state of 24
   rows (no power of two); no loop.
 * ``fast``: the shapes the tensor-core kernels take (width 256, heads of 64, feed-forward 512),
-  two streams, sharp attention (scores spread by about six) over a window of 40, prompts of
+  two streams, sharp attention (scores spread by about six) over a window of 44, prompts of
   hundreds of tokens, the parallel layer run twice.
 * ``recurrent``: state-space layers only (no keys or values anywhere, so the cache manager has
   no pages to hand out), one residual stream WITH connection weights, a state of one row in its
@@ -73,7 +73,7 @@ CONFIGS = {
     "fast": {
         "architecture": "Zuzadra", "vocab": 512, "width": 256, "norm": {"eps": 1e-5}, "streams": 2,
         "layers": [_layer(_ssm(8, 32, 64, groups=2, conv=4, norm_groups=4), 512),
-                   _layer(_parallel(4, 2, 64, 64, 40, 32, 100000.0, 4, 64, 0.5, 0.9, sharp=6.0), 512),
+                   _layer(_parallel(4, 2, 64, 64, 44, 32, 100000.0, 4, 64, 0.5, 0.9, sharp=6.0), 512),
                    _layer(_ssm(4, 64, 32, conv=4), 512)],
         "loop": {"start": 1, "stop": 2, "times": 2},
     },
